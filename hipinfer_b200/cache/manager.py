@@ -58,6 +58,15 @@ register_retention("full", lambda spec, q: ())
 register_retention("window", lambda spec, q: ((0, max(0, q - spec.window + 1)),))
 
 
+def _window_keep_first(spec, q):
+    """A window of `window` tokens that also keeps the first `keep_first` (in `extra`): dead is what lies between."""
+    keep = int(dict(spec.extra).get("keep_first", 0))
+    return ((keep, max(keep, q - spec.window + 1)),)
+
+
+register_retention("window_keep_first", _window_keep_first)
+
+
 @dataclass(frozen=True)
 class CacheGroupSpec:
     """What one group of layers needs. `n_layers` cache-owning layers share the group's block table; each keeps, per
@@ -76,7 +85,7 @@ class CacheGroupSpec:
     def __post_init__(self):
         if self.kind not in RETENTION:
             raise ValueError(f"cache group {self.name!r}: kind must be one of {sorted(RETENTION)}, got {self.kind!r}")
-        if self.kind == "window" and self.window <= 0:
+        if self.kind in ("window", "window_keep_first") and self.window <= 0:
             raise ValueError(f"cache group {self.name!r}: a window group needs window > 0")
         if not self.planes:
             object.__setattr__(self, "planes", (("k", self.kv_heads, self.head_dim), ("v", self.kv_heads, self.head_dim)))

@@ -1,7 +1,8 @@
 from .base import (Architecture, ConfigError, ModelConfig, config_from_dict, get_architecture, load_config,
                    register_architecture, registered_architectures, save_config, take)
 from .llama import Llama3RopeScaling, LlamaConfig
+from .torirax import DeltaMixerConfig, DiffAttentionConfig, ToriraxConfig, ToriraxLayerConfig
 
 __all__ = ["Architecture", "ConfigError", "ModelConfig", "config_from_dict", "get_architecture", "load_config",
            "register_architecture", "registered_architectures", "save_config", "take", "Llama3RopeScaling",
-           "LlamaConfig"]
+           "LlamaConfig", "DeltaMixerConfig", "DiffAttentionConfig", "ToriraxConfig", "ToriraxLayerConfig"]

@@ -81,8 +81,11 @@ def get_architecture(name: str) -> Architecture:
 
 
 def config_from_dict(d: Dict[str, Any]) -> ModelConfig:
-    """The typed configuration for a config.json dictionary, chosen by `architectures[0]`."""
+    """The typed configuration for a config.json dictionary, chosen by `architectures[0]` (or, in files that name
+    one architecture as a plain string, by `architecture`)."""
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        return get_architecture(d["architecture"]).config_cls.from_dict(d)
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
         raise ConfigError("config.json: key 'architectures' must be a non-empty list of names")
     return get_architecture(archs[0]).config_cls.from_dict(d)

@@ -117,15 +117,223 @@ HB_EXPORT int hb_rmsnorm(const float* x, const void* w, int w_dt, void* y, int y
 }
 
 // ---------------------------------------------------------------------------------------
+// Embedding with a scale and a learned position vector: out[i, :] = table[tok[i], :] * scale + ptab[pos[i], :]
+// (ptab null: no position vector). The product and the sum are 32-bit.
+// ---------------------------------------------------------------------------------------
+template <typename TE>
+__global__ void embed_pos_kernel(const TE* __restrict__ table, const TE* __restrict__ ptab, const int* __restrict__ tok,
+                                 const int* __restrict__ pos, float* __restrict__ out, int H, float scale) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const TE* src = table + (size_t)tok[blockIdx.x] * H;
+  const TE* pv = ptab ? ptab + (size_t)pos[blockIdx.x] * H : nullptr;
+  float* dst = out + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    dst[i] = __fadd_rn(__fmul_rn(hb_to_float(src[i]), scale), pv ? hb_to_float(pv[i]) : 0.f);
+}
+
+HB_EXPORT int hb_embed_pos(const void* table, const void* ptab, int table_dt, const int* tok, const int* pos, float* out,
+                           int T, int H, float scale, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (ptab && !pos) HB_FAIL("hb_embed_pos: a position table without positions");
+  HB_DISPATCH_1(table_dt, "hb_embed_pos",
+                (hb_launch(embed_pos_kernel<TA>, T, 256, 0, s, (const TA*)table, (const TA*)ptab, tok, pos, out, H, scale)));
+  HB_CHECK_LAUNCH("hb_embed_pos");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Layer norm with a weight and no bias: y = w * (x - mean) / sqrt(mean((x - mean)^2) + eps). Two sums in 32-bit
+// (the mean first, then the squared deviations from it), the result rounded once. `rows` as in RMSNorm.
+// ---------------------------------------------------------------------------------------
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                                                        TO* __restrict__ y, const int* __restrict__ rows, int H, float eps) {
+  __shared__ float sh[32];
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+  const float* xr = x + r * H;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) sum += xr[i];
+  const float mean = hb_block_sum(sum, sh) / (float)H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float d = xr[i] - mean;
+    ss = fmaf(d, d, ss);
+  }
+  const float inv = rsqrtf(hb_block_sum(ss, sh) / (float)H + eps);
+  TO* yr = y + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x; i < H; i += 256) yr[i] = hb_from_float<TO>(hb_to_float(w[i]) * ((xr[i] - mean) * inv));
+}
+
+// The same with the row in registers (H a multiple of 4, at most 256 * 4 * NV elements): one read of x.
+template <typename TW, typename TO, int NV>
+__global__ void __launch_bounds__(256) layernorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                                                            TO* __restrict__ y, const int* __restrict__ rows, int H,
+                                                            float eps) {
+  __shared__ float sh[32];
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+  const float* xr = x + r * H;
+  const int nvec = H >> 2;
+  float4 v[NV];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const int c = threadIdx.x + i * 256;
+    v[i] = c < nvec ? hb_load4(xr + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  const float mean = hb_block_sum(sum, sh) / (float)H;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+      ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+      ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+  }
+  const float inv = rsqrtf(hb_block_sum(ss, sh) / (float)H + eps);
+  TO* yr = y + (size_t)blockIdx.x * H;
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      const float4 ww = hb_load4(w + 4 * c);
+      hb_store4(yr + 4 * c, make_float4(ww.x * (v[i].x * inv), ww.y * (v[i].y * inv), ww.z * (v[i].z * inv),
+                                        ww.w * (v[i].w * inv)));
+    }
+  }
+}
+
+HB_EXPORT int hb_layernorm(const float* x, const void* w, int w_dt, void* y, int y_dt, const int* rows, int M, int H,
+                           float eps, cudaStream_t s) {
+  if (M <= 0) return 0;
+  const bool aligned = !(((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15);
+  if ((H & 3) == 0 && H <= 8192 && aligned) {
+    if (H <= 2048) {
+      HB_DISPATCH_2(w_dt, y_dt, "hb_layernorm",
+                    (hb_launch(layernorm_vec_kernel<TA, TB, 2>, M, 256, 0, s, x, (const TA*)w, (TB*)y, rows, H, eps)));
+    } else {
+      HB_DISPATCH_2(w_dt, y_dt, "hb_layernorm",
+                    (hb_launch(layernorm_vec_kernel<TA, TB, 8>, M, 256, 0, s, x, (const TA*)w, (TB*)y, rows, H, eps)));
+    }
+  } else {
+    HB_DISPATCH_2(w_dt, y_dt, "hb_layernorm",
+                  (hb_launch(layernorm_kernel<TA, TB>, M, 256, 0, s, x, (const TA*)w, (TB*)y, rows, H, eps)));
+  }
+  HB_CHECK_LAUNCH("hb_layernorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// PolyNorm: act = c1 N(z) + c2 N(z^2) + c3 N(z^3) + c0 over a row of z, powers element by element,
+// N(t) = t / sqrt(mean(t^2) + eps). z is the 32-bit result of the product before it; the three sums of
+// squares (z^2, z^4, z^6) and the combination are 32-bit; the result is rounded once.
+// ---------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256) polynorm_kernel(const float* __restrict__ z, long ldz, TO* __restrict__ act, long ld,
+                                                       int I, float c1, float c2, float c3, float c0, float eps) {
+  __shared__ float sh[32];
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const float* zr = z + (size_t)blockIdx.x * ldz;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int i = threadIdx.x; i < I; i += 256) {
+    const float v = zr[i], v2 = v * v, v3 = v2 * v;
+    s1 = fmaf(v, v, s1);
+    s2 = fmaf(v2, v2, s2);
+    s3 = fmaf(v3, v3, s3);
+  }
+  const float r1 = c1 * rsqrtf(hb_block_sum(s1, sh) / (float)I + eps);
+  const float r2 = c2 * rsqrtf(hb_block_sum(s2, sh) / (float)I + eps);
+  const float r3 = c3 * rsqrtf(hb_block_sum(s3, sh) / (float)I + eps);
+  TO* ar = act + (size_t)blockIdx.x * ld;
+  for (int i = threadIdx.x; i < I; i += 256) {
+    const float v = zr[i], v2 = v * v;
+    ar[i] = hb_from_float<TO>(fmaf(r1, v, fmaf(r2, v2, fmaf(r3, v2 * v, c0))));
+  }
+}
+
+HB_EXPORT int hb_polynorm(const float* z, long ldz, void* act, int act_dt, long ld, int M, int I, float c1, float c2,
+                          float c3, float c0, float eps, cudaStream_t s) {
+  if (M <= 0) return 0;
+  HB_DISPATCH_1(act_dt, "hb_polynorm",
+                (hb_launch(polynorm_kernel<TA>, M, 256, 0, s, z, ldz, (TA*)act, ld, I, c1, c2, c3, c0, eps)));
+  HB_CHECK_LAUNCH("hb_polynorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// x[m, n] += scale[n] * y[m, n]: a sublayer's result times the layer's scale vector, added into the
+// 32-bit residual stream (one product, one sum, both 32-bit).
+// ---------------------------------------------------------------------------------------
+template <typename TS>
+__global__ void scale_add_kernel(float* __restrict__ x, const float* __restrict__ y, long ldy, const TS* __restrict__ scale,
+                                 int M, int H) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)M * H) return;
+  const size_t m = i / H, n = i - m * H;
+  x[i] = __fadd_rn(x[i], __fmul_rn(hb_to_float(scale[n]), y[m * ldy + n]));
+}
+
+HB_EXPORT int hb_scale_add(float* x, const float* y, long ldy, const void* scale, int scale_dt, int M, int H,
+                           cudaStream_t s) {
+  if (M <= 0) return 0;
+  const size_t n = (size_t)M * H;
+  HB_DISPATCH_1(scale_dt, "hb_scale_add",
+                (hb_launch(scale_add_kernel<TA>, (unsigned)((n + 255) / 256), 256, 0, s, x, y, ldy, (const TA*)scale, M, H)));
+  HB_CHECK_LAUNCH("hb_scale_add");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// y = act(x + bias) over columns [c0, c0 + n) of 32-bit rows, into a matrix of its own: act 0 nothing, 1 tanh.
+// (The small middle of a low-rank projection pair.)
+// ---------------------------------------------------------------------------------------
+template <typename TB_, typename TO>
+__global__ void bias_act_kernel(const float* __restrict__ x, long ldx, const TB_* __restrict__ bias, TO* __restrict__ y,
+                                long ldy, int M, int n, int act) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)M * n) return;
+  const size_t m = i / n, c = i - m * n;
+  float v = x[m * ldx + c] + (bias ? hb_to_float(bias[c]) : 0.f);
+  if (act == 1) v = tanhf(v);
+  y[m * ldy + c] = hb_from_float<TO>(v);
+}
+
+HB_EXPORT int hb_bias_act(const float* x, long ldx, const void* bias, int bias_dt, void* y, int y_dt, long ldy, int M,
+                          int n, int act, cudaStream_t s) {
+  if (M <= 0 || n <= 0) return 0;
+  if (act < 0 || act > 1) HB_FAIL("hb_bias_act: unknown activation %d", act);
+  const size_t tot = (size_t)M * n;
+  HB_DISPATCH_2(bias_dt, y_dt, "hb_bias_act",
+                (hb_launch(bias_act_kernel<TA, TB>, (unsigned)((tot + 255) / 256), 256, 0, s, x, ldx, (const TA*)bias,
+                           (TB*)y, ldy, M, n, act)));
+  HB_CHECK_LAUNCH("hb_bias_act");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
 // Plain matrix product C[M,N] = A[M,K] W[N,K]^T, W row-major with K contiguous as the
 // reference stores weights (src/api.cu:81-83). 64x64 tile, 16 deep, 4x4 outputs per thread,
 // one FFMA chain per output running k = 0..K-1 in order: an output's value does not depend on
 // M, on the tile it lies in, or on anything else in the batch.
-// EPI 0: C = acc;  EPI 1: C += acc (32-bit C: the residual stream).
+// EPI 0: C = acc;  EPI 1: C += acc (32-bit C: the residual stream);  EPI 2: C += colscale[n] * acc (the same with
+// a scale vector over the output columns, 32-bit or the weight's element type).
 // ---------------------------------------------------------------------------------------
 template <typename TA, typename TW, typename TC, int EPI>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W,
-                                                        long ldw, TC* __restrict__ C, long ldc, int M, int N, int K) {
+                                                        long ldw, TC* __restrict__ C, long ldc, int M, int N, int K,
+                                                        const TW* __restrict__ colscale = nullptr) {
   __shared__ float As[16][68], Ws[16][68];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int m_blk = blockIdx.y * 64, n_blk = blockIdx.x * 64;
@@ -160,7 +368,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A
       const int n = n_blk + tx * 4 + j;
       if (n >= N) continue;
       TC* c = C + (size_t)m * ldc + n;
-      if (EPI == 1) *c = hb_from_float<TC>(hb_to_float(*c) + acc[i][j]);
+      if (EPI == 2) *c = hb_from_float<TC>(__fadd_rn(hb_to_float(*c), __fmul_rn(hb_to_float(colscale[n]), acc[i][j])));
+      else if (EPI == 1) *c = hb_from_float<TC>(hb_to_float(*c) + acc[i][j]);
       else *c = hb_from_float<TC>(acc[i][j]);
     }
   }
@@ -168,9 +377,13 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A
 
 template <typename TA, typename TW>
 static int gemm_simt_launch(const void* A, long lda, const void* W, long ldw, void* C, int c_dt, long ldc, int M, int N,
-                            int K, int epi, cudaStream_t s) {
+                            int K, int epi, cudaStream_t s, const void* colscale = nullptr) {
   dim3 grid((N + 63) / 64, (M + 63) / 64);
-  if (epi == 1) {
+  if (epi == 2) {
+    if (c_dt != HB_F32 || !colscale) HB_FAIL("hb_gemm_simt: the scaled sum needs a 32-bit C and a scale vector");
+    gemm_simt_kernel<TA, TW, float, 2><<<grid, 256, 0, s>>>((const TA*)A, lda, (const TW*)W, ldw, (float*)C, ldc, M, N, K,
+                                                            (const TW*)colscale);
+  } else if (epi == 1) {
     if (c_dt != HB_F32) HB_FAIL("hb_gemm_simt: accumulating into C needs a 32-bit C");
     gemm_simt_kernel<TA, TW, float, 1><<<grid, 256, 0, s>>>((const TA*)A, lda, (const TW*)W, ldw, (float*)C, ldc, M, N, K);
   } else if (c_dt == HB_F32) {
@@ -181,6 +394,20 @@ static int gemm_simt_launch(const void* A, long lda, const void* W, long ldw, vo
   } else {
     HB_FAIL("hb_gemm_simt: unknown C dtype code %d", c_dt);
   }
+  return 0;
+}
+
+// colscale (epilogue 2 only): N values of the weight's element type.
+HB_EXPORT int hb_gemm_simt_scaled(const void* A, int a_dt, long lda, const void* W, int w_dt, long ldw, float* C, long ldc,
+                                  int M, int N, int K, const void* colscale, cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) HB_FAIL("hb_gemm_simt_scaled: K must be positive");
+  if ((M + 63) / 64 > 65535) HB_FAIL("hb_gemm_simt_scaled: M = %d is beyond the grid limit", M);
+  int r = -1;
+  HB_DISPATCH_2(a_dt, w_dt, "hb_gemm_simt_scaled",
+                (r = gemm_simt_launch<TA, TB>(A, lda, W, ldw, C, HB_F32, ldc, M, N, K, 2, s, colscale)));
+  if (r) return r;
+  HB_CHECK_LAUNCH("hb_gemm_simt_scaled");
   return 0;
 }
 
@@ -343,6 +570,50 @@ HB_EXPORT int hb_rope_kv(const void* qkv, int qkv_dt, long ld, const int* pos, c
                 (rope_kv_kernel<TA, TB, TB><<<T, 256, 0, s>>>((const TA*)qkv, ld, pos, slot_map, (const float2*)table,
                                                               (TB*)q_out, (TB*)kc, (TB*)vc, Hq, Hkv, D, rot, page_size)));
   HB_CHECK_LAUNCH("hb_rope_kv");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// The cache write of a mixer without a position encoding, with biases and with keys and values of widths of their
+// own: row t of the 32-bit projection result is [q (nq) | k (G * kw) | v (G * vw)]; q + bq goes to q_out, k + bk and
+// v + bv to the token's page slot (cache planes [page][G][page_size][kw] and [...][vw]). The sums are 32-bit and
+// rounded once. No slot map (a layer that reads another layer's cache): the row is q alone.
+// ---------------------------------------------------------------------------------------
+template <typename TB_, typename TQ>
+__global__ void __launch_bounds__(256) qkv_bias_store_kernel(const float* __restrict__ qkv, long ld, const TB_* __restrict__ bq,
+                                                             const TB_* __restrict__ bk, const TB_* __restrict__ bv,
+                                                             const int* __restrict__ slot_map, TQ* __restrict__ q_out,
+                                                             TQ* __restrict__ kc, TQ* __restrict__ vc, int nq, int G, int kw,
+                                                             int vw, int page_size) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int t = blockIdx.x;
+  const float* row = qkv + (size_t)t * ld;
+  for (int i = threadIdx.x; i < nq; i += 256)
+    q_out[(size_t)t * nq + i] = hb_from_float<TQ>(row[i] + (bq ? hb_to_float(bq[i]) : 0.f));
+  const int slot = slot_map ? slot_map[t] : -1;
+  if (slot < 0) return;
+  const size_t page = slot / page_size, off = slot % page_size;
+  for (int i = threadIdx.x; i < G * kw; i += 256) {
+    const int h = i / kw, d = i - h * kw;
+    kc[((page * G + h) * page_size + off) * kw + d] = hb_from_float<TQ>(row[nq + i] + (bk ? hb_to_float(bk[i]) : 0.f));
+  }
+  for (int i = threadIdx.x; i < G * vw; i += 256) {
+    const int h = i / vw, d = i - h * vw;
+    vc[((page * G + h) * page_size + off) * vw + d] = hb_from_float<TQ>(row[nq + G * kw + i] + (bv ? hb_to_float(bv[i]) : 0.f));
+  }
+}
+
+HB_EXPORT int hb_qkv_bias_store(const float* qkv, long ld, const void* bq, const void* bk, const void* bv, int bias_dt,
+                                const int* slot_map, void* q_out, void* kc, void* vc, int q_dt, int T, int nq, int G, int kw,
+                                int vw, int page_size, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (slot_map && (!kc || !vc || G <= 0 || kw <= 0 || vw <= 0 || page_size <= 0))
+    HB_FAIL("hb_qkv_bias_store: a slot map without caches or sizes");
+  HB_DISPATCH_2(bias_dt, q_dt, "hb_qkv_bias_store",
+                (hb_launch(qkv_bias_store_kernel<TA, TB>, T, 256, 0, s, qkv, ld, (const TA*)bq, (const TA*)bk, (const TA*)bv,
+                           slot_map, (TB*)q_out, (TB*)kc, (TB*)vc, nq, G, kw, vw, page_size)));
+  HB_CHECK_LAUNCH("hb_qkv_bias_store");
   return 0;
 }
 

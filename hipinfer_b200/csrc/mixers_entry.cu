@@ -1,0 +1,17 @@
+// Error reporting of the `mixers` library (sequence mixers beyond plain attention: the delta-rule recurrence, and
+// attention with a window, kept first tokens and several score maps).
+#include "common.cuh"
+
+#include <stdarg.h>
+
+static thread_local char g_err[512];
+void hb_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+}
+HB_EXPORT const char* hb_last_error() { return g_err; }
+HB_EXPORT int hb_mixers_abi_version() { return 1; }
+int g_hb_pdl = 1;
+HB_EXPORT void hb_set_pdl(int on) { g_hb_pdl = on; }

@@ -32,6 +32,19 @@ _SIGS = {
         "hb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p],
         "hb_convert": [_p, _i, _p, _i, _l, _p],
         "hb_feed_tokens": [_p, _p, _p, _i, _p],
+        "hb_embed_pos": [_p, _p, _i, _p, _p, _p, _i, _i, _f, _p],
+        "hb_layernorm": [_p, _p, _i, _p, _i, _p, _i, _i, _f, _p],
+        "hb_polynorm": [_p, _l, _p, _i, _l, _i, _i, _f, _f, _f, _f, _f, _p],
+        "hb_scale_add": [_p, _p, _l, _p, _i, _i, _i, _p],
+        "hb_bias_act": [_p, _l, _p, _i, _p, _i, _l, _i, _i, _i, _p],
+        "hb_qkv_bias_store": [_p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+        "hb_gemm_simt_scaled": [_p, _i, _l, _p, _i, _l, _p, _l, _i, _i, _i, _p, _p],
+    },
+    "mixers": {
+        "hb_delta_rule": [_p, _l, _i, _i, _i, _i, _i, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _f,
+                          _i, _p],
+        "hb_attn_window": [_p, _i, _p, _p, _i, _p, _i, _p, _p, _p, _l, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f,
+                           _f, _i, _p],
     },
 }
 _fn_cache = {}
@@ -108,6 +121,139 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> t
     assert out.dtype == torch.float32 and out.is_contiguous() and tokens.dtype == torch.int32
     assert table.is_contiguous() and table.shape[1] == H and tokens.numel() == T
     _call("core", "hb_embed", table.data_ptr(), _dt(table), tokens.data_ptr(), out.data_ptr(), T, H, _stream())
+    return out
+
+
+def embedding_scaled(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
+                     position_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = table[tokens[i]] * scale (+ position_table[positions[i]]) into the float32 residual stream."""
+    _need_cuda(table, tokens, out, position_table, positions)
+    T, H = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and tokens.dtype == torch.int32
+    assert table.is_contiguous() and table.shape[1] == H and tokens.numel() == T
+    if position_table is not None:
+        assert position_table.dtype == table.dtype and position_table.is_contiguous() and position_table.shape[1] == H
+        assert positions is not None and positions.dtype == torch.int32 and positions.numel() == T
+    _call("core", "hb_embed_pos", table.data_ptr(), _ptr(position_table), _dt(table), tokens.data_ptr(), _ptr(positions),
+          out.data_ptr(), T, H, float(scale), _stream())
+    return out
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = weight * (x[r] - mean) / sqrt(var + eps), r = rows[i] or i; x float32 [*, H]; no bias."""
+    _need_cuda(x, weight, out, rows)
+    M, H = out.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and x.shape[1] == H
+    assert weight.numel() == H and weight.is_contiguous()
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == M
+    else:
+        assert x.shape[0] == M
+    _call("core", "hb_layernorm", x.data_ptr(), weight.data_ptr(), _dt(weight), out.data_ptr(), _dt(out), _ptr(rows),
+          M, H, float(eps), _stream())
+    return out
+
+
+def polynorm(z: torch.Tensor, coef, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = coef[0] N(z) + coef[1] N(z^2) + coef[2] N(z^3) + coef[3] row by row, N(t) = t / rms(t); z float32."""
+    _need_cuda(z, out)
+    _rows_contiguous(z, "polynorm in")
+    _rows_contiguous(out, "polynorm out")
+    assert z.dtype == torch.float32 and z.shape == out.shape and len(coef) == 4
+    M, I = out.shape
+    _call("core", "hb_polynorm", z.data_ptr(), z.stride(0), out.data_ptr(), _dt(out), out.stride(0), M, I,
+          float(coef[0]), float(coef[1]), float(coef[2]), float(coef[3]), float(eps), _stream())
+    return out
+
+
+def scale_add(x: torch.Tensor, y: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """x[m, n] += scale[n] * y[m, n]; x, y float32."""
+    _need_cuda(x, y, scale)
+    _rows_contiguous(y, "scale_add y")
+    assert x.dtype == y.dtype == torch.float32 and x.is_contiguous() and x.shape == y.shape
+    assert scale.numel() == x.shape[1] and scale.is_contiguous()
+    _call("core", "hb_scale_add", x.data_ptr(), y.data_ptr(), y.stride(0), scale.data_ptr(), _dt(scale), x.shape[0],
+          x.shape[1], _stream())
+    return x
+
+
+def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, act: str = "none") -> torch.Tensor:
+    """out = act(x + bias) for float32 rows x (a view of some columns is fine); act "none" or "tanh"."""
+    _need_cuda(x, bias, out)
+    _rows_contiguous(x, "bias_act in")
+    _rows_contiguous(out, "bias_act out")
+    assert x.dtype == torch.float32 and x.shape == out.shape
+    M, n = x.shape
+    _call("core", "hb_bias_act", x.data_ptr(), x.stride(0), _ptr(bias), _dt(bias) if bias is not None else 0,
+          out.data_ptr(), _dt(out), out.stride(0), M, n, {"none": 0, "tanh": 1}[act], _stream())
+    return out
+
+
+def qkv_bias_store(qkv: torch.Tensor, bq, bk, bv, slot_map: Optional[torch.Tensor], q_out: torch.Tensor,
+                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], n_q: int, kv_heads: int,
+                   k_width: int, v_width: int, page_size: int) -> torch.Tensor:
+    """Rows [q | k | v] of a float32 projection (+ biases): q to q_out [T, n_q], k and v to their page slots (planes
+    [page, kv_heads, page_size, width]); no position encoding. slot_map None: the rows hold q alone."""
+    _need_cuda(qkv, bq, bk, bv, slot_map, q_out, k_cache, v_cache)
+    _rows_contiguous(qkv, "qkv_bias_store in")
+    T = qkv.shape[0]
+    assert qkv.dtype == torch.float32 and q_out.is_contiguous() and q_out.shape == (T, n_q)
+    bias_dt = _dt(next((b for b in (bq, bk, bv) if b is not None), q_out))
+    if slot_map is not None:
+        assert qkv.shape[1] == n_q + kv_heads * (k_width + v_width)
+        assert k_cache.dtype == v_cache.dtype == q_out.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    else:
+        assert qkv.shape[1] == n_q
+    _call("core", "hb_qkv_bias_store", qkv.data_ptr(), qkv.stride(0), _ptr(bq), _ptr(bk), _ptr(bv), bias_dt, _ptr(slot_map),
+          q_out.data_ptr(), _ptr(k_cache) if slot_map is not None else None, _ptr(v_cache) if slot_map is not None else None,
+          _dt(q_out), T, n_q, kv_heads, k_width, v_width, page_size, _stream())
+    return q_out
+
+
+def delta_rule(proj: torch.Tensor, offsets, w_raw: torch.Tensor, w_bias, a_bias, norm_weight, state: torch.Tensor, batch,
+               out: torch.Tensor, heads: int, dim: int, decay_scale: float, unit_eps: float, eps: float,
+               force_any: bool = False) -> torch.Tensor:
+    """The generalized delta rule over the step's rows, request by request, from and into each request's state slot
+    (csrc/delta_rule.cu). proj float32 [T, *] holds r, k, v, the removal rate's and the gate's pre-activations at the
+    column `offsets` (r, k, v, a, g); w_raw float32 [T, heads * dim] the decay's; state float32 [slots, heads, dim, dim]."""
+    _need_cuda(proj, w_raw, w_bias, a_bias, norm_weight, state, out)
+    _rows_contiguous(proj, "delta_rule proj")
+    _rows_contiguous(w_raw, "delta_rule w_raw")
+    assert proj.dtype == w_raw.dtype == state.dtype == torch.float32 and state.is_contiguous() and out.is_contiguous()
+    assert state.shape[1:] == (heads, dim, dim) and out.shape == (proj.shape[0], heads * dim)
+    assert w_bias.dtype == a_bias.dtype == norm_weight.dtype
+    r, k, v, a, g = (int(o) for o in offsets)
+    _call("mixers", "hb_delta_rule", proj.data_ptr(), proj.stride(0), r, k, v, a, g, w_raw.data_ptr(), w_raw.stride(0),
+          w_bias.data_ptr(), a_bias.data_ptr(), norm_weight.data_ptr(), _dt(w_bias), state.data_ptr(),
+          batch.req_q_start.data_ptr(), batch.req_q_len.data_ptr(), batch.req_state_slot.data_ptr(), out.data_ptr(),
+          _dt(out), batch.n_requests, heads, dim, float(decay_scale), float(unit_eps), float(eps), 1 if force_any else 0,
+          _stream())
+    return out
+
+
+def attention_window(q, k_cache, v_cache, batch, group: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
+                     maps: int, page_size: int, window: int, keep_first: int, scale: float, lam: float = 0.0,
+                     post: float = 1.0, eps: float = 0.0, norm: bool = False, gate: Optional[torch.Tensor] = None,
+                     gate_offset: int = 0) -> torch.Tensor:
+    """Attention of the step's rows over their requests' pages with a window that keeps the first tokens, `maps` score
+    maps per head (2: out = a0 - lam * a1), keys `dim` and values `vdim` wide, the head's result optionally divided by
+    its root mean square and times `post`, and times sigmoid(gate[:, gate_offset + ...]) (float32) where a gate is given
+    (csrc/attention_window.cu)."""
+    _need_cuda(q, k_cache, v_cache, out, gate)
+    T = q.shape[0]
+    bt = batch.block_tables[group]
+    assert q.is_contiguous() and out.is_contiguous() and out.dtype == q.dtype == k_cache.dtype == v_cache.dtype
+    assert q.shape[1] == n_heads * maps * dim and out.shape == (T, n_heads * vdim)
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape[-1] == maps * dim and v_cache.shape[-1] == vdim
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == T
+    _call("mixers", "hb_attn_window", q.data_ptr(), _dt(q), k_cache.data_ptr(), v_cache.data_ptr(), _dt(k_cache),
+          bt.data_ptr(), bt.stride(0), batch.row_request.data_ptr(), batch.positions.data_ptr(), _ptr(gate),
+          gate.stride(0) if gate is not None else 0, int(gate_offset), out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim,
+          maps, page_size, int(window), int(keep_first), float(scale), float(lam), float(post), float(eps),
+          1 if norm else 0, _stream())
     return out
 
 
@@ -344,6 +490,29 @@ def linear(a: torch.Tensor, w: Weight, out: torch.Tensor, accumulate: bool = Fal
     if fast.linear(a, w, out, accumulate):
         return out
     return gemm_plain(a, w.t, out, accumulate)
+
+
+def linear_scaled_add(a: torch.Tensor, w: Weight, x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """x[m, n] += scale[n] * (a @ w.T)[m, n]: an output projection times the layer's scale vector, added into the float32
+    residual stream. One kernel with the plain product; the tensor-core product leaves its float32 result to a small
+    kernel that scales and adds."""
+    from . import fast
+
+    M, N = a.shape[0], w.shape[0]
+    if fast._tc_ok(a, w.t):
+        y = torch.empty(M, N, dtype=torch.float32, device=a.device)
+        fast.linear(a, w, y, False)
+        return scale_add(x, y, scale)
+    _need_cuda(a, x, scale)
+    _rows_contiguous(a, "gemm a")
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.shape == (M, N) and scale.numel() == N
+    if scale.dtype != w.t.dtype:
+        y = torch.empty(M, N, dtype=torch.float32, device=a.device)
+        gemm_plain(a, w.t, y)
+        return scale_add(x, y, scale)
+    _call("core", "hb_gemm_simt_scaled", a.data_ptr(), _dt(a), a.stride(0), w.t.data_ptr(), _dt(w.t), w.t.stride(0),
+          x.data_ptr(), x.stride(0), M, N, a.shape[1], scale.data_ptr(), _stream())
+    return x
 
 
 def linear_swiglu(a: torch.Tensor, w_gate_up: Weight, act_out: torch.Tensor, group: int) -> torch.Tensor:

@@ -1,5 +1,7 @@
 from .decoder import DecoderModel, StepCachePlan
 from . import llama  # noqa: F401  (registers LlamaForCausalLM)
+from . import torirax  # noqa: F401  (registers Torirax)
 from .llama import llama_spec
+from .torirax import torirax_spec
 
-__all__ = ["DecoderModel", "StepCachePlan", "llama_spec"]
+__all__ = ["DecoderModel", "StepCachePlan", "llama_spec", "torirax_spec"]

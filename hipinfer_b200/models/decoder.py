@@ -31,7 +31,7 @@ class DecoderModel:
         spec.validate()
         self.spec, self.ctx = spec, ctx
         self.embedding = build_part("embedding", spec.embedding, ctx)
-        self.layers = [build_part("block", PartSpec(ls.block, {"layer": ls}), ctx, ls.prefix) for ls in spec.layers]
+        self.layers = [build_part("block", PartSpec(ls.block, {**ls.params, "layer": ls}), ctx, ls.prefix) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, ctx)
         self.head = build_part("head", spec.head, ctx)
         self._plan_cache()
@@ -94,7 +94,10 @@ class DecoderModel:
     # ---------------------------------------------------------------- forward
     def forward(self, batch, storage) -> torch.Tensor:
         """Run the batch's tokens from the cache; logits float32 [len(batch.want_rows), vocab]."""
-        x = self.embedding.forward(batch.tokens)
+        if getattr(self.embedding, "takes_positions", False):
+            x = self.embedding.forward(batch.tokens, batch.positions)
+        else:
+            x = self.embedding.forward(batch.tokens)
         planes.record(batch, "embedding", x)
         # what a layer leaves for the next reader of x: a sum not yet added (kernels.ops.Pending: the next norm adds
         # it), or that next norm already prepared by the layer's last product (kernels.fast.NormFeed); else None

@@ -7,9 +7,12 @@ with a message. Every block has an attribute `mixer`: the part whose `cache_need
 `state_need()` the cache manager serves."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
+from ..weights import ParamSpec
 from . import planes
-from .registry import Part, build_part, register_part
+from .registry import Part, build_part, register_part, to_compute
 
 
 def build_slots(block: Part, layer, slots, ctx, prefix) -> list:
@@ -111,4 +114,68 @@ class PreNormBlock(Part):
         return None
 
 
+class ScaledPreNormBlock(Part):
+    """Pre-norm with layer scale: x += s1 * mixer(norm(x)); x += s2 * feed_forward(norm(x)), s1 and s2 vectors over the
+    width that multiply each sublayer's result before the sum. The feed-forward (with its norm and scale) is optional:
+    a layer that gives no `feed_forward` part has the first sublayer only.
+
+    params: layer (the LayerSpec), hidden_size, mixer_scale_name, feed_forward_scale_name (tensor names relative to the
+    prefix). A part that sets `takes_out_scale` multiplies by the vector in its own last product (`out_scale=`); any
+    other part writes into a zeroed buffer, which is then scaled and added here."""
+
+    SLOTS = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+    OPTIONAL = ("feed_forward_norm", "feed_forward")
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        layer = params["layer"]
+        has_ff = "feed_forward" in layer.parts
+        slots = {n: r for n, r in self.SLOTS.items() if has_ff or n not in self.OPTIONAL}
+        self.parts = build_slots(self, layer, slots, ctx, prefix)
+        if not has_ff:
+            self.feed_forward = self.feed_forward_norm = None
+        self.hidden = int(params.get("hidden_size", getattr(self.mixer_norm, "size", 0)))
+        self.scale_names = [prefix + params.get("mixer_scale_name", "ls1")]
+        if has_ff:
+            self.scale_names.append(prefix + params.get("feed_forward_scale_name", "ls2"))
+        self.scales = [None, None]
+
+    def param_specs(self):
+        return [s for p in self.parts for s in p.param_specs()] + [ParamSpec(n, (self.hidden,), init="ones") for n in self.scale_names]
+
+    def load(self, tensors):
+        for p in self.parts:
+            p.load(tensors)
+        for i, n in enumerate(self.scale_names):
+            self.scales[i] = to_compute(tensors[n], self.ctx)
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self.parts) + sum(s.numel() * s.element_size() for s in self.scales if s is not None)
+
+    def _sublayer(self, part, scale, xn, x, *rest):
+        if getattr(part, "takes_out_scale", False):
+            left = part.forward(xn, x, *rest, out_scale=scale)
+            if isinstance(left, ops.Pending):
+                left.finish()
+            return
+        y = torch.zeros_like(x)
+        left = part.forward(xn, y, *rest)
+        if isinstance(left, ops.Pending):
+            left.finish()
+        ops.scale_add(x, y, scale)
+
+    def forward(self, x, batch, cache, state):
+        xn = self.mixer_norm.forward(x)
+        planes.record(batch, "mixer_norm", xn)
+        self._sublayer(self.mixer, self.scales[0], xn, x, batch, cache, state)
+        planes.record(batch, "after_mixer", x)
+        if self.feed_forward is not None:
+            xn = self.feed_forward_norm.forward(x)
+            planes.record(batch, "feed_forward_norm", xn)
+            self._sublayer(self.feed_forward, self.scales[1], xn, x, batch)
+        planes.record(batch, "after_feed_forward", x)
+        return None
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "pre_norm_scaled", ScaledPreNormBlock)

@@ -29,6 +29,37 @@ class TokenEmbedding(Part):
         return ops.embedding(self.table, tokens, x)
 
 
+class ScaledPositionEmbedding(Part):
+    """x = table[token] * scale + position_table[position]: a scaled token embedding and a learned vector per absolute
+    position (not scaled). params: name, vocab_size, hidden_size, scale (default 1), position_name (absent: no position
+    vectors), max_position. The decoder hands it the step's positions (`takes_positions`)."""
+
+    takes_positions = True
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        self.name, self.vocab, self.hidden = params["name"], int(params["vocab_size"]), int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))
+        self.position_name = params.get("position_name")
+        self.max_position = int(params.get("max_position", 0))
+        self.table = self.position_table = None
+
+    def param_specs(self):
+        specs = [ParamSpec(self.name, (self.vocab, self.hidden))]
+        if self.position_name:
+            specs.append(ParamSpec(self.position_name, (self.max_position, self.hidden)))
+        return specs
+
+    def load(self, tensors):
+        self.table = to_compute(tensors[self.name], self.ctx)
+        if self.position_name:
+            self.position_table = to_compute(tensors[self.position_name], self.ctx).to(self.table.dtype)
+
+    def forward(self, tokens, positions):
+        x = torch.empty(tokens.numel(), self.hidden, dtype=torch.float32, device=tokens.device)
+        return ops.embedding_scaled(self.table, tokens, x, self.scale, self.position_table, positions)
+
+
 class LMHead(Part):
     """params: name (its own tensor) or tied_to (the embedding's tensor name), vocab_size, hidden_size."""
 
@@ -56,4 +87,5 @@ class LMHead(Part):
 
 
 register_part("embedding", "token", TokenEmbedding)
+register_part("embedding", "token_position", ScaledPositionEmbedding)
 register_part("head", "linear", LMHead)

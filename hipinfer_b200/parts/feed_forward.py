@@ -62,4 +62,48 @@ class SwiGLU(Part):
         return ops.linear_deferred(act, self.wdown, x, accumulate=True)   # the next norm may add it
 
 
+class PolyNormFF(Part):
+    """A dense feed-forward without a gate: out = act(xn Wup^T) Wdown^T with the PolyNorm activation
+    act(z) = c1 N(z) + c2 N(z^2) + c3 N(z^3) + c0, powers element by element, N(t) = t / sqrt(mean(t^2) + eps) over
+    the row's `intermediate_size` values. The four coefficients are a tensor [c1, c2, c3, c0]. The up product stays in
+    32-bit until after the activation (the three root mean squares are 32-bit sums), which is rounded once.
+
+    params: hidden_size, intermediate_size, eps, up_name, down_name, act_name. With `out_scale=` (a vector over the
+    output columns) the result is multiplied by it before it is added into the residual stream."""
+
+    takes_out_scale = True
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        self.hidden, self.inter, self.eps = int(params["hidden_size"]), int(params["intermediate_size"]), float(params["eps"])
+        self.names = {k: prefix + params.get(k + "_name", f"mlp.{k}") for k in ("up", "down", "act")}
+        self.wup = self.wdown = self.coef = None
+
+    def param_specs(self):
+        return [ParamSpec(self.names["up"], (self.inter, self.hidden)), ParamSpec(self.names["down"], (self.hidden, self.inter)),
+                ParamSpec(self.names["act"], (4,), init="ones")]
+
+    def load(self, tensors):
+        self.wup = ops.Weight(to_compute(tensors[self.names["up"]], self.ctx))
+        self.wdown = ops.Weight(to_compute(tensors[self.names["down"]], self.ctx))
+        self.coef = [float(v) for v in tensors[self.names["act"]].float().cpu().tolist()]
+
+    def weight_bytes(self):
+        return self.wup.nbytes + self.wdown.nbytes
+
+    def forward(self, xn, x, batch, out_scale=None):
+        T = xn.shape[0]
+        z = torch.empty(T, self.inter, dtype=torch.float32, device=xn.device)
+        ops.linear(xn, self.wup, z)
+        act = torch.empty(T, self.inter, dtype=self.ctx.dtype, device=xn.device)
+        ops.polynorm(z, self.coef, self.eps, act)
+        planes.record(batch, "activation", act)
+        if out_scale is None:
+            ops.linear(act, self.wdown, x, accumulate=True)
+        else:
+            ops.linear_scaled_add(act, self.wdown, x, out_scale)
+        return None
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "polynorm", PolyNormFF)

@@ -53,4 +53,31 @@ class RMSNorm(Part):
         return ops.rmsnorm(x, self.weight, self.eps, out, rows, pending)
 
 
+class LayerNorm(Part):
+    """Layer norm with a weight and no bias: y = w * (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps), computed in 32-bit
+    from the 32-bit residual stream and rounded once. params: name (tensor name relative to the prefix), size, eps."""
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        self.size, self.eps = int(params["size"]), float(params["eps"])
+        self.name = prefix + params["name"]
+        self.weight = None
+
+    def param_specs(self):
+        return [ParamSpec(self.name, (self.size,), init="ones")]
+
+    def load(self, tensors):
+        self.weight = to_compute(tensors[self.name], self.ctx)
+
+    def weight_bytes(self):
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, x, rows=None, out=None):
+        M = x.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = torch.empty(M, self.size, dtype=self.ctx.dtype, device=x.device)
+        return ops.layernorm(x, self.weight, self.eps, out, rows)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

@@ -32,6 +32,7 @@ class LayerSpec:
     prefix: str                       # tensor-name prefix of the layer, e.g. "model.layers.3."
     block: str                        # arrangement kind
     parts: Mapping[str, PartSpec]     # slot name -> part; the block kind says which slots it has
+    params: Mapping[str, Any] = field(default_factory=dict)   # constants of the arrangement itself (a block with none ignores it)
 
     def part(self, slot: str) -> PartSpec:
         try:

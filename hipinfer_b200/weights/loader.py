@@ -35,6 +35,7 @@ class ParamSpec:
     init: str = "normal"
     optional: bool = False
     numbers: str = "float"       # "float": a weight (any float type in the file); "int": a table of integers
+    free: Tuple[int, ...] = ()   # axes whose size the file decides (shape holds what the random-weights mode draws)
 
 
 class WeightError(ValueError):
@@ -81,7 +82,10 @@ def check_names(folder: str, specs: Sequence[ParamSpec], have: Dict[str, Tuple[i
     ignore = set(ignore)
     missing = [n for n, s in want.items() if n not in have and not s.optional]
     unexpected = [n for n in have if n not in want and n not in ignore]
-    wrong = [(n, have[n], s.shape) for n, s in want.items() if n in have and tuple(have[n]) != tuple(s.shape)]
+    def fits(got, s):
+        return len(got) == len(s.shape) and all(g == w or (i in s.free and g > 0) for i, (g, w) in enumerate(zip(got, s.shape)))
+
+    wrong = [(n, have[n], s.shape) for n, s in want.items() if n in have and not fits(tuple(have[n]), s)]
     wrong_dt = []
     for n, s in want.items():
         if dtypes is None or n not in dtypes:
