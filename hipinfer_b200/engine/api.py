@@ -57,6 +57,8 @@ class Engine:
                              ("heads", "num_attention_heads"), ("kv_heads", "num_key_value_heads"),
                              ("head_dim", "head_dim"), ("tied", "tie_word_embeddings")):
             setattr(self, ours, getattr(c, theirs, None))
+        if self.layers is None:            # an architecture whose configuration lists its layers one by one
+            self.layers = len(r.spec.layers)
         self.weight_bytes = r.model.step_weight_bytes()
         self.kv_bytes_per_token = r.storage.bytes_per_token()
         # pipeline: a step is launched before the tokens of the step before it have been read
