@@ -428,6 +428,130 @@ def breakdown(layers: int, batch: int, prefill: bool = False) -> int:
     return 0
 
 
+# ------------------------------------------------------------------------------------------
+# --design torirax: the Torirax design beside the Llama decoder at equal layer sizes (random weights)
+# ------------------------------------------------------------------------------------------
+DESIGN_SIZES = {
+    # width, layers, heads, kv heads, feed-forward, vocabulary: the 1B and (with 8 of its 32 layers) the 8B Llama layer sizes
+    "1b": dict(width=2048, layers=16, heads=32, kv=8, head_dim=64, ff=8192, vocab=128256),
+    "8b": dict(width=4096, layers=8, heads=32, kv=8, head_dim=128, ff=14336, vocab=128256),
+}
+
+
+def design_configs(size: dict, window: int):
+    """(Torirax config, Llama config) of equal width, depth, head counts and feed-forward width. Torirax alternates a
+    delta-rule layer (heads x head_dim, no feed-forward) and a differential-attention layer whose two score maps
+    together are as wide as a Llama head (dim = head_dim / 2 each, values head_dim), with the feed-forward; every
+    second attention layer reads the cache of the one before it."""
+    W, L, H, G, D = size["width"], size["layers"], size["heads"], size["kv"], size["head_dim"]
+    layers, last_owner = [], None
+    for i in range(L):
+        if i % 2 == 0:
+            layers.append(dict(type="general_delta", mixer=dict(heads=H, dim=D, decay_rank=64), mlp=None))
+        else:
+            m = dict(heads=H, kv_heads=G, dim=D // 2, vdim=D, scale=(D // 2) ** -0.5, diff=0.5, mask=dict(size=window, keep_first=4))
+            if last_owner is not None and (i // 2) % 2 == 1:
+                m["kv_from"] = last_owner
+            else:
+                last_owner = i
+            layers.append(dict(type="attention", mixer=m, mlp=dict(kind="dense", ff=size["ff"])))
+    torirax = dict(architecture="Torirax", vocab=size["vocab"], width=W, max_positions=CONTEXT_LEN, embedding=dict(scale=1.0),
+                   norm=dict(eps=1e-5), layers=layers)
+    llama = dict(MODEL, vocab_size=size["vocab"], hidden_size=W, intermediate_size=size["ff"], num_hidden_layers=L,
+                 num_attention_heads=H, num_key_value_heads=G, head_dim=D, tie_word_embeddings=False)
+    return torirax, llama
+
+
+def kernel_table(one, reps: int = 3):
+    """{kernel name: (launches, microseconds)} of one call of `one` (the middle of `reps` profiled calls)."""
+    import json as _json
+    import tempfile
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    for _ in range(3):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(reps):
+            one()
+        torch.cuda.synchronize()
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "trace.json")
+        prof.export_chrome_trace(path)
+        with open(path) as f:
+            events = sorted((e for e in _json.load(f)["traceEvents"] if e.get("cat") == "kernel"), key=lambda e: e["ts"])
+    per = len(events) // reps
+    agg = {}
+    for e in events[per:2 * per]:
+        a = agg.setdefault(e["name"].split("(")[0][:60], [0, 0.0])
+        a[0] += 1
+        a[1] += e["dur"]
+    return {k: (c, round(us, 1)) for k, (c, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])}
+
+
+def design_bench(a) -> int:
+    """Prefill and decode throughput of the Torirax design and of the Llama decoder at equal layer sizes, with each
+    step's kernels by name; one JSON line. The default run of this file is untouched by this option."""
+    import torch
+
+    from hipinfer_b200 import Engine
+    from hipinfer_b200.engine import StepEntry
+    from hipinfer_b200.kernels import ops
+
+    global PROMPT_LEN, PREFILL_TOKENS
+    PROMPT_LEN, PREFILL_TOKENS = a.prompt, a.prefill_tokens
+    out = {"design": "torirax", "beside": "llama", "dtype": "bf16", "data": "synthetic: random token ids, random weights",
+           "prompt": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS, "window": a.window, "sizes": {}}
+    clocks = ClockSampler().start()
+    batches = [1, 8, 64]
+    for name in a.sizes.split(","):
+        size = dict(DESIGN_SIZES[name])
+        if a.layers:
+            size["layers"] = a.layers
+        MODEL["vocab_size"] = size["vocab"]
+        res = {}
+        for which, cfg in zip(("torirax", "llama"), design_configs(size, a.window)):
+            pages_per_seq = -(-(PROMPT_LEN + a.steps + a.warmup + 16 + 4 * PAGE) // PAGE)
+            eng = Engine(config=cfg, random_weights=0, std=0.02, dtype="bfloat16", max_batch=max(batches), max_seq=CONTEXT_LEN,
+                         max_prefill=max(PREFILL_TOKENS, PROMPT_LEN), page_size=PAGE,
+                         num_pages=max(batches) * pages_per_seq + 8)
+            r = {"weight_gb": round(eng.weight_bytes / 1e9, 3)}
+            pre_ms = prefill_device(eng, 3, 5)
+            r["prefill"] = {"ms": round(pre_ms, 3), "tok_s": round(PREFILL_TOKENS / pre_ms * 1e3, 1)}
+            for b in batches:
+                ms = statistics.median(decode_device(eng, b, min(a.steps, 64), a.warmup)[0] for _ in range(3))
+                r[f"decode_b{b}"] = {"ms": round(ms, 4), "tok_s": round(b / ms * 1e3, 1)}
+            if not a.no_points:
+                runner = eng.runner
+                toks, count = prompts(1, 3, PREFILL_TOKENS)[0], [0]
+
+                def one_prefill():
+                    count[0] += 1
+                    runner.step([StepEntry(("kt", count[0]), toks, [PREFILL_TOKENS - 1])])
+                    runner.end(("kt", count[0]))
+
+                r["prefill_kernels"] = kernel_table(one_prefill)
+                ids = [("kd", i) for i in range(8)]
+                first = [ops.sample(runner.step([StepEntry(rid, p, [PROMPT_LEN - 1])]), None, None, None)
+                         for rid, p in zip(ids, prompts(8, 1))]
+                tokens = torch.cat(first).contiguous()
+                entries = [StepEntry(rid, [0], [0]) for rid in ids]
+                r["decode_b8_kernels"] = kernel_table(
+                    lambda: ops.sample(runner.step(entries, device_tokens=tokens), None, None, None, out=tokens))
+                for rid in ids:
+                    runner.end(rid)
+            eng.close()
+            del eng
+            torch.cuda.empty_cache()
+            res[which] = r
+        out["sizes"][name] = dict(size, **res)
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm(a) -> int:
     """The unmodified reference through its own binding (baseline/reference_arm.py builds it with its
     own make line and drives `Engine.prefill` / `Engine.decode`): the same metric, sizes, steps and
@@ -508,6 +632,11 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     ap.add_argument("--breakdown", action="store_true", help="print per-kernel times of a decode step and exit")
     ap.add_argument("--prefill", action="store_true", help="with --breakdown: the prefill step instead of a decode step")
+    ap.add_argument("--design", default=None, choices=["torirax"],
+                    help="prefill and decode of this design beside the Llama decoder at equal layer sizes (see --sizes); "
+                         "the default run is not changed by it")
+    ap.add_argument("--sizes", default="1b", help="with --design: layer sizes, of " + ", ".join(sorted(DESIGN_SIZES)) + " (commas between)")
+    ap.add_argument("--window", type=int, default=1024, help="with --design: the attention window (the first 4 tokens are kept)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
@@ -520,6 +649,10 @@ def main() -> int:
         choose_shape(a.shape, a.prompt, a.prefill_tokens, a.steps + a.warmup + 8)
     if a.layers is None:
         a.layers = MODEL["num_hidden_layers"]
+    if a.design:
+        if a.warmup < 3:
+            a.warmup = 3
+        return design_bench(a)
     if a.breakdown:
         return breakdown(a.layers, a.batch, a.prefill)
     if a.workload == "mixed":

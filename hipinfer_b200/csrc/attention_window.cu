@@ -32,6 +32,8 @@ struct WinArgs {
   int H, G, D, E, M, page_size, window, keep_first;
   float scale, lambda, post, eps;
   int norm;             // divide the head's result by its root mean square
+  const int* q_len;     // [R] or null: rows of requests that bring row_limit rows or more are left to the flash kernel
+  int row_limit;
 };
 
 template <typename TQ, typename TC>
@@ -40,6 +42,7 @@ __global__ void __launch_bounds__(128) attn_window_kernel(WinArgs A) {
   hb_pdl_launch();
   hb_pdl_wait();
   const int g = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (A.q_len && A.q_len[A.row_req[t]] >= A.row_limit) return;
   const int H = A.H, G = A.G, D = A.D, E = A.E, M = A.M, HG = H / G, R = HG * M, ps = A.page_size;
   float* qs = smem;              // [R][D]
   float* sc = qs + R * D;        // [R][KT]
@@ -138,7 +141,8 @@ __global__ void __launch_bounds__(128) attn_window_kernel(WinArgs A) {
 HB_EXPORT int hb_attn_window(const void* q, int q_dt, const void* kc, const void* vc, int cache_dt, const int* bt,
                              int bt_stride, const int* row_req, const int* pos, const float* gate, long ld_gate,
                              int gate_off, void* out, int T, int H, int G, int D, int E, int M, int page_size, int window,
-                             int keep_first, float scale, float lambda, float post, float eps, int norm, cudaStream_t s) {
+                             int keep_first, float scale, float lambda, float post, float eps, int norm, const int* q_len,
+                             int row_limit, cudaStream_t s) {
   if (T <= 0) return 0;
   if (G <= 0 || H % G) HB_FAIL("hb_attn_window: %d query heads are not a multiple of %d kv heads", H, G);
   if (M != 1 && M != 2) HB_FAIL("hb_attn_window: %d score maps (1 or 2)", M);
@@ -149,7 +153,7 @@ HB_EXPORT int hb_attn_window(const void* q, int q_dt, const void* kc, const void
   const size_t smem = ((size_t)R * (D + KT + E + 3) + KT) * sizeof(float);
   if (smem > 200 * 1024) HB_FAIL("hb_attn_window: %d score rows of %d + %d need %zu bytes of shared memory", R, D, E, smem);
   WinArgs A{q, kc, vc, bt, bt_stride, row_req, pos, gate, ld_gate, gate_off, out, H, G, D, E, M, page_size, window, keep_first,
-            scale, lambda, post, eps, norm};
+            scale, lambda, post, eps, norm, q_len, row_limit};
   HB_DISPATCH_1(q_dt, "hb_attn_window", {
     auto kern = attn_window_kernel<TA, TA>;
     if (smem > 48 * 1024) {

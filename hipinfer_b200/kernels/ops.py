@@ -44,7 +44,10 @@ _SIGS = {
         "hb_delta_rule": [_p, _l, _i, _i, _i, _i, _i, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _f,
                           _i, _p],
         "hb_attn_window": [_p, _i, _p, _p, _i, _p, _i, _p, _p, _p, _l, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f,
-                           _f, _i, _p],
+                           _f, _i, _p, _i, _p],
+        "hb_attn_window_flash": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f,
+                                 _f, _f, _i, _p],
+        "hb_attn_window_flash_supported": [_i, _i, _i, _i, _i],
     },
 }
 _fn_cache = {}
@@ -232,10 +235,13 @@ def delta_rule(proj: torch.Tensor, offsets, w_raw: torch.Tensor, w_bias, a_bias,
     return out
 
 
+WINDOW_FLASH_MIN_ROWS = 16     # requests that bring at least this many rows go to the flash kernel of attention_window
+
+
 def attention_window(q, k_cache, v_cache, batch, group: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
                      maps: int, page_size: int, window: int, keep_first: int, scale: float, lam: float = 0.0,
                      post: float = 1.0, eps: float = 0.0, norm: bool = False, gate: Optional[torch.Tensor] = None,
-                     gate_offset: int = 0) -> torch.Tensor:
+                     gate_offset: int = 0, force_rows: bool = False) -> torch.Tensor:
     """Attention of the step's rows over their requests' pages with a window that keeps the first tokens, `maps` score
     maps per head (2: out = a0 - lam * a1), keys `dim` and values `vdim` wide, the head's result optionally divided by
     its root mean square and times `post`, and times sigmoid(gate[:, gate_offset + ...]) (float32) where a gate is given
@@ -249,11 +255,27 @@ def attention_window(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
     assert k_cache.shape[-1] == maps * dim and v_cache.shape[-1] == vdim
     if gate is not None:
         assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == T
+    gate_ld = gate.stride(0) if gate is not None else 0
+    # requests that bring WINDOW_FLASH_MIN_ROWS rows or more go to the tensor-core kernel (bfloat16, two maps, the sizes it
+    # takes), the other rows of the step to the row kernel; a decode-only step is the row kernel alone
+    from . import fast
+
+    flash = (maps == 2 and norm and q.dtype == torch.bfloat16 and not fast.PLAIN_ONLY and not force_rows
+             and getattr(batch, "max_q_len", 0) >= WINDOW_FLASH_MIN_ROWS
+             and _fn("mixers", "hb_attn_window_flash_supported")(n_heads, n_kv_heads, dim, vdim, maps) == 1
+             and (gate is None or (gate_ld % 2 == 0 and gate_offset % 2 == 0)))
+    if flash:
+        _call("mixers", "hb_attn_window_flash", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), bt.data_ptr(), bt.stride(0),
+              batch.req_q_start.data_ptr(), batch.req_q_len.data_ptr(), batch.req_ctx_len.data_ptr(), _ptr(gate), gate_ld,
+              int(gate_offset), out.data_ptr(), batch.n_requests, batch.max_q_len, n_heads, n_kv_heads, dim, vdim, page_size,
+              int(window), int(keep_first), float(scale), float(lam), float(post), float(eps), WINDOW_FLASH_MIN_ROWS, _stream())
+        if min(batch.h_q_len) >= WINDOW_FLASH_MIN_ROWS:
+            return out
     _call("mixers", "hb_attn_window", q.data_ptr(), _dt(q), k_cache.data_ptr(), v_cache.data_ptr(), _dt(k_cache),
-          bt.data_ptr(), bt.stride(0), batch.row_request.data_ptr(), batch.positions.data_ptr(), _ptr(gate),
-          gate.stride(0) if gate is not None else 0, int(gate_offset), out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim,
-          maps, page_size, int(window), int(keep_first), float(scale), float(lam), float(post), float(eps),
-          1 if norm else 0, _stream())
+          bt.data_ptr(), bt.stride(0), batch.row_request.data_ptr(), batch.positions.data_ptr(), _ptr(gate), gate_ld,
+          int(gate_offset), out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim, maps, page_size, int(window), int(keep_first),
+          float(scale), float(lam), float(post), float(eps), 1 if norm else 0,
+          batch.req_q_len.data_ptr() if flash else None, WINDOW_FLASH_MIN_ROWS, _stream())
     return out
 
 

@@ -204,7 +204,8 @@ def _paged(k, v, G, ps, seed):
     return kc, vc, perm.to(torch.int32)
 
 
-def _attend(dtype, H, G, D, E, M, n_keys, q_pos, window, keep, ps, plant=(), lam=0.7, c=0.4, gate=True, seed=0, drop_dead=True):
+def _attend(dtype, H, G, D, E, M, n_keys, q_pos, window, keep, ps, plant=(), lam=0.7, c=0.4, gate=True, seed=0, drop_dead=True,
+            portion=False):
     """Rows at positions q_pos over n_keys keys; `plant`: (row, key position) whose score is made to stand out in BOTH maps.
     Pages that no row can see are taken out of the block table (-1), as the cache manager does. Returns (got, want)."""
     from hipinfer_b200.kernels import ops
@@ -225,6 +226,11 @@ def _attend(dtype, H, G, D, E, M, n_keys, q_pos, window, keep, ps, plant=(), lam
                 bt[lp] = -1
     batch = SimpleNamespace(block_tables=[bt.view(1, -1).to(DEV)], row_request=torch.zeros(T, dtype=torch.int32, device=DEV),
                             positions=torch.tensor(q_pos, dtype=torch.int32, device=DEV))
+    if portion:        # the rows are one request's portion: what the tensor-core kernel is told about it
+        assert list(q_pos) == list(range(q_pos[0], q_pos[0] + T))
+        i32 = lambda v: torch.tensor([v], dtype=torch.int32, device=DEV)
+        batch.req_q_start, batch.req_q_len, batch.req_ctx_len = i32(0), i32(T), i32(q_pos[0])
+        batch.h_q_len, batch.max_q_len, batch.n_requests = [T], T, 1
     out = torch.empty(T, H * E, dtype=dtype, device=DEV)
     scale = 1.0 / math.sqrt(D)
     ops.attention_window(q.reshape(T, -1).to(DEV), kc.to(DEV), vc.to(DEV), batch, 0, out, H, G, D, E, M, ps, window or 0, keep,
@@ -278,3 +284,22 @@ def test_a_planted_key_decides_the_result_when_seen_only():
         v = rnd(600, 1, 8, seed=j + 3)[j, 0].double()
         dist = float((got.double().cpu().view(8) / 0.6 - v).abs().max())
         assert (dist < 1e-3) == seen, (j, dist)
+
+
+@pytest.mark.parametrize("D, E", [(32, 64), (64, 128), (128, 64), (32, 128), (64, 64), (128, 128)])
+@pytest.mark.parametrize("window, keep, ctx, n", [(70, 3, 0, 200), (100, 5, 333, 130), (64, 64, 200, 64), (1, 1, 10, 17),
+                                                  (None, 0, 50, 100), (500, 2, 600, 16)])
+def test_window_attention_portions_on_tensor_cores(D, E, window, keep, ctx, n):
+    """A portion of n rows behind ctx cached tokens through the flash kernel (bfloat16): windows shorter and longer than a
+    key tile, kept tokens within and beyond the first tile, a portion that ends inside a query tile, planted keys at the
+    window's edge of the first, a middle and the last row."""
+    rows = (0, n // 2, n - 1)
+    plant = [(r, ctx + r - window + 1) for r in rows if window and ctx + r - window + 1 >= 0]
+    plant += [(r, ctx + r - window) for r in rows[1:] if window and ctx + r - window >= keep]
+    got, want = _attend(torch.bfloat16, 4, 2, D, E, 2, ctx + n, list(range(ctx, ctx + n)), window, keep, 16, plant=plant,
+                        seed=D + E + n, portion=True)
+    close(got, want, torch.bfloat16)
+    # and the row kernel on the same rows: the two paths differ by rounding only
+    got_rows, _ = _attend(torch.bfloat16, 4, 2, D, E, 2, ctx + n, list(range(ctx, ctx + n)), window, keep, 16, plant=plant,
+                          seed=D + E + n)
+    close(got, got_rows.double().cpu(), torch.bfloat16, "flash against rows")

@@ -57,7 +57,7 @@ def test_tensor_list_and_the_rank_the_file_decides():
     assert "l3.mix.k" not in specs and "l3.mix.v.b" not in specs and "l3.mix.q" in specs      # the reader has no k/v
     assert "l0.norm2" not in specs and "l0.ls2" not in specs and "l1.ls2" in specs            # no feed-forward, no second norm
     assert specs["l1.mix.q"].shape == (8 * 2 * 32, 128) and specs["l1.mix.k"].shape == (2 * 2 * 32, 128)
-    assert specs["l1.mix.v"].shape == (2 * 48, 128) and specs["l1.mix.o"].shape == (128, 8 * 48)
+    assert specs["l1.mix.v"].shape == (2 * 64, 128) and specs["l1.mix.o"].shape == (128, 8 * 64)
     assert specs["l2.mix.w1"].shape == (24, 128) and specs["l2.mix.w1"].free == ()
     assert specs["l0.mix.w1"].free == (0,) and specs["l0.mix.w2"].free == (1,)
     have = {n: tuple(s.shape) for n, s in specs.items()}
@@ -76,7 +76,7 @@ def test_cache_plan_shares_and_retains_the_widest_look_back():
     assert plan[1].write and not plan[3].write and (plan[3].group, plan[3].slot) == (plan[1].group, plan[1].slot)
     g = m.cache_groups[plan[1].group]
     assert g.kind == "window_keep_first" and g.window == 130 and dict(g.extra)["keep_first"] == 5      # the reader's, wider
-    assert g.planes == (("k", 2, 64), ("v", 2, 48))
+    assert g.planes == (("k", 2, 64), ("v", 2, 64))
     assert [o.reads_cache_of for o in spec.order] == [None, None, None, 1, None]
     # no window anywhere: everything is kept
     c, spec = _spec(tm.Q)

@@ -40,8 +40,9 @@ Q = model(97, 48, [attn(3, 3, 8, 8, ff=80), delta(1, 48, ff=56, rank=5), attn(2,
           max_positions=300, scale=1.0, eps=1e-6)
 # R: wider: delta heads of 64 and of 128, a group of 4, windows that cross pages and the attention kernel's key tiles,
 #    a reader with a LONGER window and more kept tokens than the layer that writes the cache
-R = model(211, 128, [delta(2, 64), attn(8, 2, 32, 48, window=70, keep=2, ff=192), delta(1, 128, rank=24),
-                     attn(8, 2, 32, 48, window=130, keep=5, kv_from=1), attn(4, 4, 16, 16, window=64, keep=64, ff=64)],
+#    (heads of 32 with values of 64: in bfloat16 the attention of portions runs on the tensor-core kernel)
+R = model(211, 128, [delta(2, 64), attn(8, 2, 32, 64, window=70, keep=2, ff=192), delta(1, 128, rank=24),
+                     attn(8, 2, 32, 64, window=130, keep=5, kv_from=1), attn(4, 4, 16, 16, window=64, keep=64, ff=64)],
           max_positions=700, scale=3.0)
 
 MODELS = {"p": P, "q": Q, "r": R}
