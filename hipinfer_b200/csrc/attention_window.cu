@@ -138,11 +138,176 @@ __global__ void __launch_bounds__(128) attn_window_kernel(WinArgs A) {
   }
 }
 
+// The same for a bfloat16 cache whose rows are whole 16-byte chunks (M * D and E multiples of 8) and at most 16 score
+// rows: a tile's keys and values are gathered into shared memory with cp.async (16 bytes a copy, the next tile while
+// this one is worked on), so that global memory is read once and in whole rows; a thread owns one key of the tile and
+// every second score row (with two maps: the rows of one map), and reads its key 8 elements at a time. The arithmetic
+// is that of the kernel above in the same order (the score's sum runs over d = 0 .. D-1 in one chain), so a row gets
+// the same bits from either.
+__device__ __forceinline__ void win_cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+constexpr int WS_THREADS = 512, WS_PARTS = WS_THREADS / KT;     // 16 warps: one block fills an SM's schedulers
+
+__global__ void __launch_bounds__(WS_THREADS) attn_window_staged_kernel(WinArgs A) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int g = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (A.q_len && A.q_len[A.row_req[t]] >= A.row_limit) return;
+  const int H = A.H, G = A.G, D = A.D, E = A.E, M = A.M, HG = H / G, R = HG * M, ps = A.page_size;
+  const int KW = M * D, KP = KW + 8;          // a key row in shared memory is 16 bytes longer: rows fall on different banks
+  __nv_bfloat16* Kt = (__nv_bfloat16*)smem_raw;                 // [2][KT][KP]
+  __nv_bfloat16* Vt = Kt + 2 * KT * KP;                         // [2][KT][E]
+  float* qs = (float*)(Vt + 2 * KT * E);                        // [R][D]
+  float* sc = qs + R * D;                                       // [R][KT]
+  float* acc = sc + R * KT;                                     // [R][E]
+  float* mrun = acc + R * E;
+  float* lrun = mrun + R;
+  float* alpha = lrun + R;
+  const int p = A.pos[t];
+  const int lo = A.window > 0 ? max(0, p - A.window + 1) : 0;
+  const int keep = A.window > 0 ? min(A.keep_first, p + 1) : 0;
+  const int* table = A.bt + (size_t)A.row_req[t] * A.bt_stride;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)A.kc;
+  const __nv_bfloat16* vc = (const __nv_bfloat16*)A.vc;
+  const int last_tile = p / KT, first_win_tile = lo / KT, last_keep_tile = keep > 0 ? (keep - 1) / KT : -1;
+  const int ck = KW / 8, cv = E / 8;
+
+  auto load_tile = [&](int buf, int ti) {
+    const int k0 = ti * KT;
+    __nv_bfloat16* kd = Kt + buf * KT * KP;
+    __nv_bfloat16* vd = Vt + buf * KT * E;
+    for (int i = tid; i < KT * (ck + cv); i += WS_THREADS) {
+      const int r = i / (ck + cv), c = i - r * (ck + cv), kp = k0 + r;
+      const bool vis = kp <= p && (kp >= lo || kp < keep);
+      __nv_bfloat16* dst = c < ck ? kd + r * KP + c * 8 : vd + r * E + (c - ck) * 8;
+      if (vis) {
+        const size_t row = ((size_t)table[kp / ps] * G + g) * ps + kp % ps;
+        win_cp16((uint32_t)__cvta_generic_to_shared(dst), c < ck ? kc + row * KW + c * 8 : vc + row * E + (c - ck) * 8);
+      } else {
+        *(uint4*)dst = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+
+  int ti = last_keep_tile >= 0 ? 0 : first_win_tile;
+  load_tile(0, ti);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  const __nv_bfloat16* qrow = (const __nv_bfloat16*)A.q + ((size_t)t * H + (size_t)g * HG) * M * D;
+  for (int i = tid; i < R * D; i += WS_THREADS) qs[i] = __bfloat162float(qrow[i]) * A.scale;
+  for (int i = tid; i < R * E; i += WS_THREADS) acc[i] = 0.f;
+  if (tid < R) { mrun[tid] = -INFINITY; lrun[tid] = 0.f; }   // (R <= 16 < WS_THREADS)
+
+  for (int it = 0; ti <= last_tile; it++) {
+    const int buf = it & 1;
+    const int next = (ti == last_keep_tile && ti + 1 < first_win_tile) ? first_win_tile : ti + 1;
+    if (next <= last_tile) load_tile(buf ^ 1, next);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    const int k0 = ti * KT;
+    {
+      // thread = (key j of the tile, part): score rows part and part + WS_PARTS (with two maps both are rows of map part % 2)
+      const int j = tid & (KT - 1), part = tid >> 6, kp = k0 + j;
+      const bool vis = kp <= p && (kp >= lo || kp < keep);
+      const __nv_bfloat16* krow = Kt + (buf * KT + j) * KP + (part % M) * D;
+      float a[2] = {0.f, 0.f};
+      for (int c = 0; c < D / 8; c++) {
+        const uint4 raw = *(const uint4*)(krow + c * 8);
+        const __nv_bfloat162* h2 = (const __nv_bfloat162*)&raw;
+        float kf[8];
+#pragma unroll
+        for (int x = 0; x < 4; x++) { const float2 f = __bfloat1622float2(h2[x]); kf[2 * x] = f.x; kf[2 * x + 1] = f.y; }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+          const int r = part + WS_PARTS * i;
+          if (r < R) {
+            const float4* qr = (const float4*)(qs + r * D + c * 8);
+            const float4 q0 = qr[0], q1 = qr[1];
+            a[i] = fmaf(q0.x, kf[0], a[i]); a[i] = fmaf(q0.y, kf[1], a[i]); a[i] = fmaf(q0.z, kf[2], a[i]); a[i] = fmaf(q0.w, kf[3], a[i]);
+            a[i] = fmaf(q1.x, kf[4], a[i]); a[i] = fmaf(q1.y, kf[5], a[i]); a[i] = fmaf(q1.z, kf[6], a[i]); a[i] = fmaf(q1.w, kf[7], a[i]);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int r = part + WS_PARTS * i;
+        if (r < R) sc[r * KT + j] = vis ? a[i] : -INFINITY;
+      }
+    }
+    __syncthreads();
+    for (int r = warp; r < R; r += WS_THREADS / 32) {
+      float m = -INFINITY;
+      for (int j = lane; j < KT; j += 32) m = fmaxf(m, sc[r * KT + j]);
+      m = fmaxf(hb_warp_max(m), mrun[r]);
+      float l = 0.f;
+      for (int j = lane; j < KT; j += 32) {
+        const float e = expf(sc[r * KT + j] - m);
+        sc[r * KT + j] = e;
+        l += e;
+      }
+      l = hb_warp_sum(l);
+      if (lane == 0) {
+        const float al = expf(mrun[r] - m);
+        alpha[r] = al;
+        lrun[r] = fmaf(lrun[r], al, l);
+        mrun[r] = m;
+      }
+    }
+    __syncthreads();
+    {
+      // a thread owns value column e of TWO score rows (one read of a value serves both), four keys a step; a key
+      // that is not visible has weight 0 and a zeroed row of values, so it adds nothing
+      const __nv_bfloat16* vt = Vt + buf * KT * E;
+      const int RP = (R + 1) >> 1;
+      for (int i = tid; i < RP * E; i += WS_THREADS) {
+        const int rp = i / E, e = i - rp * E, r0 = 2 * rp, r1 = min(r0 + 1, R - 1);
+        const float4* p0 = (const float4*)(sc + r0 * KT);
+        const float4* p1 = (const float4*)(sc + r1 * KT);
+        float a0 = acc[r0 * E + e] * alpha[r0], a1 = acc[r1 * E + e] * alpha[r1];
+#pragma unroll 4
+        for (int j4 = 0; j4 < KT / 4; j4++) {
+          const float4 w0 = p0[j4], w1 = p1[j4];
+          const float v0 = __bfloat162float(vt[(4 * j4) * E + e]), v1 = __bfloat162float(vt[(4 * j4 + 1) * E + e]);
+          const float v2 = __bfloat162float(vt[(4 * j4 + 2) * E + e]), v3 = __bfloat162float(vt[(4 * j4 + 3) * E + e]);
+          a0 = fmaf(w0.x, v0, a0); a0 = fmaf(w0.y, v1, a0); a0 = fmaf(w0.z, v2, a0); a0 = fmaf(w0.w, v3, a0);
+          a1 = fmaf(w1.x, v0, a1); a1 = fmaf(w1.y, v1, a1); a1 = fmaf(w1.z, v2, a1); a1 = fmaf(w1.w, v3, a1);
+        }
+        acc[r0 * E + e] = a0;
+        if (r1 != r0) acc[r1 * E + e] = a1;
+      }
+    }
+    __syncthreads();
+    ti = next;
+  }
+  for (int hg = warp; hg < HG; hg += WS_THREADS / 32) {
+    const int r0 = hg * M;
+    const float l0 = lrun[r0], l1 = M > 1 ? lrun[r0 + 1] : 1.f;
+    float ss = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      float o = acc[r0 * E + e] / l0;
+      if (M > 1) o = o - A.lambda * (acc[(r0 + 1) * E + e] / l1);
+      acc[r0 * E + e] = o;
+      ss = fmaf(o, o, ss);
+    }
+    ss = hb_warp_sum(ss);
+    const float f = A.norm ? rsqrtf(ss / (float)E + A.eps) * A.post : A.post;
+    const size_t head = (size_t)t * H + (size_t)g * HG + hg;
+    for (int e = lane; e < E; e += 32) {
+      float o = acc[r0 * E + e] * f;
+      if (A.gate) o *= 1.f / (1.f + expf(-A.gate[(size_t)t * A.ld_gate + A.gate_off + (g * HG + hg) * E + e]));
+      ((__nv_bfloat16*)A.out)[head * E + e] = __float2bfloat16_rn(o);
+    }
+  }
+}
+
 HB_EXPORT int hb_attn_window(const void* q, int q_dt, const void* kc, const void* vc, int cache_dt, const int* bt,
                              int bt_stride, const int* row_req, const int* pos, const float* gate, long ld_gate,
                              int gate_off, void* out, int T, int H, int G, int D, int E, int M, int page_size, int window,
                              int keep_first, float scale, float lambda, float post, float eps, int norm, const int* q_len,
-                             int row_limit, cudaStream_t s) {
+                             int row_limit, int force_plain, cudaStream_t s) {
   if (T <= 0) return 0;
   if (G <= 0 || H % G) HB_FAIL("hb_attn_window: %d query heads are not a multiple of %d kv heads", H, G);
   if (M != 1 && M != 2) HB_FAIL("hb_attn_window: %d score maps (1 or 2)", M);
@@ -154,6 +319,17 @@ HB_EXPORT int hb_attn_window(const void* q, int q_dt, const void* kc, const void
   if (smem > 200 * 1024) HB_FAIL("hb_attn_window: %d score rows of %d + %d need %zu bytes of shared memory", R, D, E, smem);
   WinArgs A{q, kc, vc, bt, bt_stride, row_req, pos, gate, ld_gate, gate_off, out, H, G, D, E, M, page_size, window, keep_first,
             scale, lambda, post, eps, norm, q_len, row_limit};
+  const size_t staged = (size_t)2 * KT * (M * D + 8 + E) * 2 + ((size_t)R * (D + KT + E + 3)) * sizeof(float);
+  if (q_dt == HB_BF16 && !force_plain && (M * D) % 8 == 0 && E % 8 == 0 && D % 8 == 0 && R <= 16 && staged <= 200 * 1024 &&
+      !(((uintptr_t)kc | (uintptr_t)vc) & 15)) {
+    if (staged > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(attn_window_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged);
+      if (e != cudaSuccess) HB_FAIL("hb_attn_window: %s", cudaGetErrorString(e));
+    }
+    hb_launch(attn_window_staged_kernel, dim3(G, T), WS_THREADS, staged, s, A);
+    HB_CHECK_LAUNCH("hb_attn_window");
+    return 0;
+  }
   HB_DISPATCH_1(q_dt, "hb_attn_window", {
     auto kern = attn_window_kernel<TA, TA>;
     if (smem > 48 * 1024) {

@@ -15,8 +15,8 @@
 // and how many tokens comes from device arrays (first row, row count and state slot of each request), so the
 // launch is the same for every batch of as many requests and replays from a CUDA graph.
 //
-//   delta_rule_kernel      TPC threads share a value channel, each with NR = D / TPC key channels of it in registers;
-//                          the two sums over key channels end with shuffles among the TPC threads (D = 32, 64, 128).
+//   delta_rule_kernel      four threads share a value channel, each with D / 4 key channels of it in registers; tokens
+//                          in chunks, what does not depend on the state a chunk at a time (D = 32, 64, 128).
 //   delta_rule_any_kernel  any D: the state in shared memory, a thread per value channel.
 #include "common.cuh"
 
@@ -104,70 +104,182 @@ __global__ void delta_rule_any_kernel(DeltaArgs A) {
   if (on) for (int i = 0; i < D; i++) Sg[i * D + j] = S[i * D + j];
 }
 
-// TPC threads per value channel, NR key channels each: D = TPC * NR, blockDim = D * TPC (lanes of a channel are
-// neighbours, so the shuffles stay inside a warp). Thread (j, q) holds S[q * NR + i][j], i < NR.
+// TPC threads per value channel, NR key channels each: D = TPC * NR, blockDim = D * TPC. Thread (q, j) holds
+// S[q * NR + i][j], i < NR, in registers; the TPC parts of a sum over key channels meet in shared memory.
+//
+// The tokens go by in chunks of DR_CH. What does not depend on the state is done for a whole chunk at once, a warp per
+// token: the unit key (one warp sum), decay and removal rate (expf), into shared memory; the raw values of the NEXT
+// chunk are already on their way from global memory while the state walks through this one. The walk itself then
+// costs, per token, 4 NR fused multiply-adds a thread, broadcast reads of the token's vectors and ONE barrier (for
+// u^T S, whose parts must meet before the state moves; the parts of the output meet after the chunk). The head norm
+// and the gate of the chunk's outputs are again a warp per token.
+constexpr int DR_CH = 16;
+
 template <typename TW, typename TO, int NR, int TPC>
 __global__ void __launch_bounds__(NR * TPC * TPC) delta_rule_kernel(DeltaArgs A) {
-  constexpr int D = NR * TPC, NT = D * TPC, NW = NT / 32;
-  __shared__ float vr[D], vw[D], vau[D], vk[D], vu[D], sh[32];
+  constexpr int D = NR * TPC, NT = D * TPC, NW = NT / 32, TPW = DR_CH / NW, CPL = D / 32;
+  static_assert(TPW >= 1 && TPW * NW == DR_CH && CPL >= 1 && NR % 4 == 0, "chunk, warps and head size must fit");
+  extern __shared__ __align__(16) float dr_smem[];
+  float* vr = dr_smem;                 // [DR_CH][D] each
+  float* vw = vr + DR_CH * D;
+  float* vau = vw + DR_CH * D;
+  float* vk = vau + DR_CH * D;
+  float* vu = vk + DR_CH * D;
+  float* vv = vu + DR_CH * D;
+  float* vo = vv + DR_CH * D;          // [DR_CH][TPC][D]: the parts of a token's outputs, summed when the chunk is done
+  float* xs = vo + DR_CH * TPC * D;    // [2][TPC][D]: the parts of u^T S of the token at hand (two buffers, one barrier a token)
   hb_pdl_launch();
   hb_pdl_wait();
-  const int h = blockIdx.x, req = blockIdx.y, tid = threadIdx.x, j = tid / TPC, q = tid % TPC;
+  // a warp's lanes are 32 value channels j with the SAME part q of the key channels: what they read of the token's
+  // vectors is one address for the whole warp (a broadcast, one pass through shared memory)
+  const int h = blockIdx.x, req = blockIdx.y, tid = threadIdx.x, q = tid / D, j = tid % D, lane = tid & 31, warp = tid >> 5;
   float* Sg = A.state + ((size_t)A.slot[req] * A.heads + h) * D * D;
   float S[NR];
 #pragma unroll
   for (int i = 0; i < NR; i++) S[i] = Sg[(q * NR + i) * D + j];
   const int t0 = A.q_start[req], n = A.q_len[req];
   const TW* wb = (const TW*)A.w_bias, *ab = (const TW*)A.a_bias, *nwt = (const TW*)A.norm_w;
-  const int c = h * D + j;
-  for (int t = t0; t < t0 + n; t++) {
-    const float* row = A.proj + (size_t)t * A.ld;
-    // the first D threads prepare channel `tid` of the token's vectors
-    const int cc = h * D + tid;
-    float kj = 0.f;
-    if (tid < D) kj = row[A.k_off + cc];
-    const float kk = head_sum(kj * kj, sh, NW);
-    if (tid < D) {
-      const float uj = kj / sqrtf(kk + A.unit_eps);
-      vr[tid] = row[A.r_off + cc];
-      vw[tid] = expf(-A.decay_scale * sigmoidf_(A.w_raw[(size_t)t * A.ldw + cc] + hb_to_float(wb[cc])));
-      vau[tid] = sigmoidf_(row[A.a_off + cc] + hb_to_float(ab[cc])) * uj;
-      vk[tid] = kj;
-      vu[tid] = uj;
+  const int hc = h * D;
+
+  // raw values of a chunk's tokens: warp `warp` takes tokens warp, warp + NW, ..; a lane channels lane, lane + 32, ..
+  float pre[TPW][CPL][5];              // k, r, v, a_raw, w_raw
+  auto fetch = [&](int base) {
+#pragma unroll
+    for (int x = 0; x < TPW; x++) {
+      const int tt = warp + x * NW;
+      if (base + tt < n) {
+        const float* row = A.proj + (size_t)(t0 + base + tt) * A.ld;
+        const float* wrow = A.w_raw + (size_t)(t0 + base + tt) * A.ldw;
+#pragma unroll
+        for (int y = 0; y < CPL; y++) {
+          const int c = hc + lane + 32 * y;
+          pre[x][y][0] = row[A.k_off + c];
+          pre[x][y][1] = row[A.r_off + c];
+          pre[x][y][2] = row[A.v_off + c];
+          pre[x][y][3] = row[A.a_off + c];
+          pre[x][y][4] = wrow[c];
+        }
+      }
     }
-    const float vj = row[A.v_off + c];
+  };
+  fetch(0);
+  for (int base = 0; base < n; base += DR_CH) {
+    // the chunk's vectors into shared memory
+#pragma unroll
+    for (int x = 0; x < TPW; x++) {
+      const int tt = warp + x * NW;
+      if (base + tt < n) {                                   // (uniform over the warp)
+        float kk = 0.f;
+#pragma unroll
+        for (int y = 0; y < CPL; y++) kk = fmaf(pre[x][y][0], pre[x][y][0], kk);
+        kk = hb_warp_sum(kk);
+        const float inv = 1.f / sqrtf(kk + A.unit_eps);
+#pragma unroll
+        for (int y = 0; y < CPL; y++) {
+          const int cl = lane + 32 * y, c = hc + cl;
+          const float kj = pre[x][y][0], uj = kj * inv;
+          vk[tt * D + cl] = kj;
+          vu[tt * D + cl] = uj;
+          vr[tt * D + cl] = pre[x][y][1];
+          vv[tt * D + cl] = pre[x][y][2];
+          vau[tt * D + cl] = sigmoidf_(pre[x][y][3] + hb_to_float(ab[c])) * uj;
+          vw[tt * D + cl] = expf(-A.decay_scale * sigmoidf_(pre[x][y][4] + hb_to_float(wb[c])));
+        }
+      }
+    }
     __syncthreads();
-    float sa = 0.f;
+    if (base + DR_CH < n) fetch(base + DR_CH);               // in flight during the walk
+    const int m = min(DR_CH, n - base);
+    for (int tt = 0; tt < m; tt++) {
+      // (heads of up to 64) all of the token's vectors are asked for at once: one wait for shared memory a token
+      constexpr bool HOIST = NR <= 16;
+      const float4* up = (const float4*)(vu + tt * D + q * NR);
+      const float4* kp = (const float4*)(vk + tt * D + q * NR);
+      const float4* wp = (const float4*)(vw + tt * D + q * NR);
+      const float4* ap = (const float4*)(vau + tt * D + q * NR);
+      const float4* rp = (const float4*)(vr + tt * D + q * NR);
+      float4 u[HOIST ? NR / 4 : 1], k[HOIST ? NR / 4 : 1], w[HOIST ? NR / 4 : 1], a[HOIST ? NR / 4 : 1], r[HOIST ? NR / 4 : 1];
+      if (HOIST) {
 #pragma unroll
-    for (int i = 0; i < NR; i++) sa = fmaf(vu[q * NR + i], S[i], sa);
+        for (int i = 0; i < NR / 4; i++) { u[i] = up[i]; k[i] = kp[i]; w[i] = wp[i]; a[i] = ap[i]; r[i] = rp[i]; }
+      }
+      const float vj = vv[tt * D + j];
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-    for (int o_ = 1; o_ < TPC; o_ <<= 1) sa += __shfl_xor_sync(0xffffffffu, sa, o_);
-    float o = 0.f;
+      for (int i = 0; i < NR / 4; i++) {
+        const float4 uu = HOIST ? u[i] : up[i];
+        s0 = fmaf(uu.x, S[4 * i], s0); s1 = fmaf(uu.y, S[4 * i + 1], s1);
+        s2 = fmaf(uu.z, S[4 * i + 2], s2); s3 = fmaf(uu.w, S[4 * i + 3], s3);
+      }
+      float* x = xs + (tt & 1) * TPC * D;
+      x[q * D + j] = (s0 + s1) + (s2 + s3);
+      __syncthreads();
+      float sa = x[j];
 #pragma unroll
-    for (int i = 0; i < NR; i++) {
-      const int ki = q * NR + i;
-      S[i] = fmaf(vk[ki], vj, fmaf(vw[ki], S[i], -vau[ki] * sa));
-      o = fmaf(S[i], vr[ki], o);
+      for (int qq = 1; qq < TPC; qq++) sa += x[qq * D + j];
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < NR / 4; i++) {
+        const float4 kk = HOIST ? k[i] : kp[i], ww = HOIST ? w[i] : wp[i], aa = HOIST ? a[i] : ap[i], rr = HOIST ? r[i] : rp[i];
+        S[4 * i] = fmaf(kk.x, vj, fmaf(ww.x, S[4 * i], -aa.x * sa));             o0 = fmaf(S[4 * i], rr.x, o0);
+        S[4 * i + 1] = fmaf(kk.y, vj, fmaf(ww.y, S[4 * i + 1], -aa.y * sa));     o1 = fmaf(S[4 * i + 1], rr.y, o1);
+        S[4 * i + 2] = fmaf(kk.z, vj, fmaf(ww.z, S[4 * i + 2], -aa.z * sa));     o2 = fmaf(S[4 * i + 2], rr.z, o2);
+        S[4 * i + 3] = fmaf(kk.w, vj, fmaf(ww.w, S[4 * i + 3], -aa.w * sa));     o3 = fmaf(S[4 * i + 3], rr.w, o3);
+      }
+      vo[(tt * TPC + q) * D + j] = (o0 + o1) + (o2 + o3);
     }
+    __syncthreads();
+    // the chunk's outputs: head norm, weight and gate, a warp per token
 #pragma unroll
-    for (int o_ = 1; o_ < TPC; o_ <<= 1) o += __shfl_xor_sync(0xffffffffu, o, o_);
-    const float oo = head_sum(q == 0 ? o * o : 0.f, sh, NW);
-    if (q == 0) {
-      const float y = o * rsqrtf(oo / (float)D + A.eps) * hb_to_float(nwt[c]) * sigmoidf_(row[A.g_off + c]);
-      ((TO*)A.out)[(size_t)t * A.heads * D + c] = hb_from_float<TO>(y);
+    for (int x = 0; x < TPW; x++) {
+      const int tt = warp + x * NW;
+      if (base + tt < n) {
+        float ov[CPL], oo = 0.f;
+#pragma unroll
+        for (int y = 0; y < CPL; y++) {
+          ov[y] = vo[tt * TPC * D + lane + 32 * y];
+#pragma unroll
+          for (int qq = 1; qq < TPC; qq++) ov[y] += vo[(tt * TPC + qq) * D + lane + 32 * y];
+          oo = fmaf(ov[y], ov[y], oo);
+        }
+        oo = hb_warp_sum(oo);
+        const float f = rsqrtf(oo / (float)D + A.eps);
+        const size_t t = (size_t)(t0 + base + tt);
+        const float* row = A.proj + t * A.ld;
+#pragma unroll
+        for (int y = 0; y < CPL; y++) {
+          const int c = hc + lane + 32 * y;
+          ((TO*)A.out)[t * A.heads * D + c] = hb_from_float<TO>(ov[y] * f * hb_to_float(nwt[c]) * sigmoidf_(row[A.g_off + c]));
+        }
+      }
     }
   }
 #pragma unroll
   for (int i = 0; i < NR; i++) Sg[(q * NR + i) * D + j] = S[i];
 }
 
+template <typename TW, typename TO, int NR, int TPC>
+static int delta_rule_launch_reg(const DeltaArgs& A, dim3 grid, cudaStream_t s) {
+  constexpr int D = NR * TPC;
+  const size_t smem = ((size_t)(6 + TPC) * DR_CH * D + 2 * TPC * D) * sizeof(float);
+  auto kern = delta_rule_kernel<TW, TO, NR, TPC>;
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) HB_FAIL("hb_delta_rule: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  hb_launch(kern, grid, D * TPC, smem, s, A);
+  return 0;
+}
+
 template <typename TW, typename TO>
 static int delta_rule_launch(const DeltaArgs& A, int R, cudaStream_t s) {
   const dim3 grid(A.heads, R);
   switch (A.D) {
-    case 32: hb_launch(delta_rule_kernel<TW, TO, 8, 4>, grid, 128, 0, s, A); return 0;
-    case 64: hb_launch(delta_rule_kernel<TW, TO, 16, 4>, grid, 256, 0, s, A); return 0;
-    case 128: hb_launch(delta_rule_kernel<TW, TO, 16, 8>, grid, 1024, 0, s, A); return 0;
+    case 32: return delta_rule_launch_reg<TW, TO, 8, 4>(A, grid, s);
+    case 64: return delta_rule_launch_reg<TW, TO, 16, 4>(A, grid, s);
+    case 128: return delta_rule_launch_reg<TW, TO, 32, 4>(A, grid, s);
     default: break;
   }
   const int threads = (A.D + 31) / 32 * 32;

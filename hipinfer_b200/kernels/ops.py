@@ -44,7 +44,7 @@ _SIGS = {
         "hb_delta_rule": [_p, _l, _i, _i, _i, _i, _i, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _f,
                           _i, _p],
         "hb_attn_window": [_p, _i, _p, _p, _i, _p, _i, _p, _p, _p, _l, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f,
-                           _f, _i, _p, _i, _p],
+                           _f, _i, _p, _i, _i, _p],
         "hb_attn_window_flash": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f,
                                  _f, _f, _i, _p],
         "hb_attn_window_flash_supported": [_i, _i, _i, _i, _i],
@@ -241,7 +241,7 @@ WINDOW_FLASH_MIN_ROWS = 16     # requests that bring at least this many rows go 
 def attention_window(q, k_cache, v_cache, batch, group: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
                      maps: int, page_size: int, window: int, keep_first: int, scale: float, lam: float = 0.0,
                      post: float = 1.0, eps: float = 0.0, norm: bool = False, gate: Optional[torch.Tensor] = None,
-                     gate_offset: int = 0, force_rows: bool = False) -> torch.Tensor:
+                     gate_offset: int = 0, force_rows: bool = False, force_plain: bool = False) -> torch.Tensor:
     """Attention of the step's rows over their requests' pages with a window that keeps the first tokens, `maps` score
     maps per head (2: out = a0 - lam * a1), keys `dim` and values `vdim` wide, the head's result optionally divided by
     its root mean square and times `post`, and times sigmoid(gate[:, gate_offset + ...]) (float32) where a gate is given
@@ -275,7 +275,7 @@ def attention_window(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
           bt.data_ptr(), bt.stride(0), batch.row_request.data_ptr(), batch.positions.data_ptr(), _ptr(gate), gate_ld,
           int(gate_offset), out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim, maps, page_size, int(window), int(keep_first),
           float(scale), float(lam), float(post), float(eps), 1 if norm else 0,
-          batch.req_q_len.data_ptr() if flash else None, WINDOW_FLASH_MIN_ROWS, _stream())
+          batch.req_q_len.data_ptr() if flash else None, WINDOW_FLASH_MIN_ROWS, 1 if force_plain else 0, _stream())
     return out
 
 

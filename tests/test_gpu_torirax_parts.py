@@ -205,7 +205,7 @@ def _paged(k, v, G, ps, seed):
 
 
 def _attend(dtype, H, G, D, E, M, n_keys, q_pos, window, keep, ps, plant=(), lam=0.7, c=0.4, gate=True, seed=0, drop_dead=True,
-            portion=False):
+            portion=False, force_plain=False):
     """Rows at positions q_pos over n_keys keys; `plant`: (row, key position) whose score is made to stand out in BOTH maps.
     Pages that no row can see are taken out of the block table (-1), as the cache manager does. Returns (got, want)."""
     from hipinfer_b200.kernels import ops
@@ -234,7 +234,8 @@ def _attend(dtype, H, G, D, E, M, n_keys, q_pos, window, keep, ps, plant=(), lam
     out = torch.empty(T, H * E, dtype=dtype, device=DEV)
     scale = 1.0 / math.sqrt(D)
     ops.attention_window(q.reshape(T, -1).to(DEV), kc.to(DEV), vc.to(DEV), batch, 0, out, H, G, D, E, M, ps, window or 0, keep,
-                         scale, lam, 1.0 - c, 1e-5, M == 2, gate=g_raw.to(DEV) if gate else None, gate_offset=5)
+                         scale, lam, 1.0 - c, 1e-5, M == 2, gate=g_raw.to(DEV) if gate else None, gate_offset=5,
+                         force_plain=force_plain)
     qd, kd, vd = q.double(), k.double(), v.double()
     want = torch.zeros(T, H, E, dtype=torch.float64)
     for t, p in enumerate(q_pos):
@@ -303,3 +304,11 @@ def test_window_attention_portions_on_tensor_cores(D, E, window, keep, ctx, n):
     got_rows, _ = _attend(torch.bfloat16, 4, 2, D, E, 2, ctx + n, list(range(ctx, ctx + n)), window, keep, 16, plant=plant,
                           seed=D + E + n)
     close(got, got_rows.double().cpu(), torch.bfloat16, "flash against rows")
+
+
+@pytest.mark.parametrize("H, G, D, E, M", [(4, 2, 16, 24, 2), (8, 2, 32, 64, 2), (4, 1, 64, 128, 2), (2, 1, 40, 16, 1)])
+def test_row_kernels_with_and_without_shared_memory_tiles_give_the_same_bits(H, G, D, E, M):
+    args = (torch.bfloat16, H, G, D, E, M, 300, [0, 5, 63, 64, 200, 299], 90, 3, 16)
+    a, _ = _attend(*args, seed=4)
+    b, _ = _attend(*args, seed=4, force_plain=True)
+    assert torch.equal(a, b)
