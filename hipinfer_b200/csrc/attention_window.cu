@@ -34,6 +34,9 @@ struct WinArgs {
   int norm;             // divide the head's result by its root mean square
   const int* q_len;     // [R] or null: rows of requests that bring row_limit rows or more are left to the flash kernel
   int row_limit;
+  float* part;          // staged kernel, several key splits a row: [T][G][splits][R][E + 2] partial (sums, maximum, weight sum)
+  int* arrived;         // [T][G] zeroed counters; the block that arrives last at a (row, kv head) joins the splits and leaves 0
+  int splits;           // gridDim.z
 };
 
 template <typename TQ, typename TC>
@@ -142,12 +145,16 @@ __global__ void __launch_bounds__(128) attn_window_kernel(WinArgs A) {
 // rows: a tile's keys and values are gathered into shared memory with cp.async (16 bytes a copy, the next tile while
 // this one is worked on), so that global memory is read once and in whole rows; a thread owns one key of the tile and
 // every second score row (with two maps: the rows of one map), and reads its key 8 elements at a time. The arithmetic
-// is that of the kernel above in the same order (the score's sum runs over d = 0 .. D-1 in one chain), so a row gets
-// the same bits from either.
+// is that of the kernel above in the same order (the score's sum runs over d = 0 .. D-1 in one chain), so a row whose
+// keys one block walks gets the same bits from either. A row with more than WS_SPLIT_TILES tiles of visible keys is
+// split over several blocks (gridDim.z), each with a running maximum and sums of its own; the block that arrives last
+// joins them in the splits' order and finishes the row: a serial walk of a long window is bound by the latency of one
+// tile after the other, many short walks are not.
 __device__ __forceinline__ void win_cp16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
+constexpr int WS_SPLIT_TILES = 4;      // key tiles a block walks: a row's keys are split over blocks of this many
 constexpr int WS_THREADS = 512, WS_PARTS = WS_THREADS / KT;     // 16 warps: one block fills an SM's schedulers
 
 __global__ void __launch_bounds__(WS_THREADS) attn_window_staged_kernel(WinArgs A) {
@@ -192,7 +199,14 @@ __global__ void __launch_bounds__(WS_THREADS) attn_window_staged_kernel(WinArgs 
     }
   };
 
-  int ti = last_keep_tile >= 0 ? 0 : first_win_tile;
+  // the tiles with a visible key, in order: those of the kept tokens, then the window's; split `blockIdx.z` walks
+  // WS_SPLIT_TILES of them (which tiles a split gets depends on the row's position alone)
+  const int win0 = max(first_win_tile, last_keep_tile + 1), n_vis = (last_keep_tile + 1) + (last_tile - win0 + 1);
+  const int n_splits = (n_vis + WS_SPLIT_TILES - 1) / WS_SPLIT_TILES;
+  const int ord0 = blockIdx.z * WS_SPLIT_TILES, ord1 = min(n_vis, ord0 + WS_SPLIT_TILES);
+  if (ord0 >= n_vis) return;
+  auto tile_of = [&](int ord) { return ord <= last_keep_tile ? ord : win0 + (ord - (last_keep_tile + 1)); };
+  int ord = ord0, ti = tile_of(ord0);
   load_tile(0, ti);
   asm volatile("cp.async.commit_group;" ::: "memory");
   const __nv_bfloat16* qrow = (const __nv_bfloat16*)A.q + ((size_t)t * H + (size_t)g * HG) * M * D;
@@ -200,10 +214,10 @@ __global__ void __launch_bounds__(WS_THREADS) attn_window_staged_kernel(WinArgs 
   for (int i = tid; i < R * E; i += WS_THREADS) acc[i] = 0.f;
   if (tid < R) { mrun[tid] = -INFINITY; lrun[tid] = 0.f; }   // (R <= 16 < WS_THREADS)
 
-  for (int it = 0; ti <= last_tile; it++) {
+  for (int it = 0; ord < ord1; it++, ord++) {
     const int buf = it & 1;
-    const int next = (ti == last_keep_tile && ti + 1 < first_win_tile) ? first_win_tile : ti + 1;
-    if (next <= last_tile) load_tile(buf ^ 1, next);
+    const int next = ord + 1 < ord1 ? tile_of(ord + 1) : -1;
+    if (next >= 0) load_tile(buf ^ 1, next);
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
@@ -282,6 +296,47 @@ __global__ void __launch_bounds__(WS_THREADS) attn_window_staged_kernel(WinArgs 
     __syncthreads();
     ti = next;
   }
+  if (n_splits > 1) {
+    // leave this split's sums; the block that arrives last at the (row, kv head) joins all splits in their order
+    __shared__ int last;
+    const size_t slot = ((size_t)t * G + g) * A.splits;
+    float* mine = A.part + (slot + blockIdx.z) * R * (E + 2);
+    for (int i = tid; i < R * E; i += WS_THREADS) mine[(i / E) * (E + 2) + i % E] = acc[i];
+    if (tid < R) { mine[tid * (E + 2) + E] = mrun[tid]; mine[tid * (E + 2) + E + 1] = lrun[tid]; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int seen = atomicAdd(A.arrived + (size_t)t * G + g, 1);
+      last = seen == n_splits - 1;
+      if (last) A.arrived[(size_t)t * G + g] = 0;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    const float* all = A.part + slot * R * (E + 2);
+    if (tid < R) {
+      float m = -INFINITY;
+      for (int z = 0; z < n_splits; z++) m = fmaxf(m, __ldcg(all + ((size_t)z * R + tid) * (E + 2) + E));
+      float l = 0.f;
+      for (int z = 0; z < n_splits; z++) {
+        const float* pz = all + ((size_t)z * R + tid) * (E + 2);
+        l = fmaf(__ldcg(pz + E + 1), expf(__ldcg(pz + E) - m), l);
+      }
+      mrun[tid] = m;
+      lrun[tid] = l;
+    }
+    __syncthreads();
+    for (int i = tid; i < R * E; i += WS_THREADS) {
+      const int r = i / E, e = i - r * E;
+      float a = 0.f;
+      for (int z = 0; z < n_splits; z++) {
+        const float* pz = all + ((size_t)z * R + r) * (E + 2);
+        a = fmaf(__ldcg(pz + e), expf(__ldcg(pz + E) - mrun[r]), a);
+      }
+      acc[i] = a;
+    }
+    __syncthreads();
+  }
   for (int hg = warp; hg < HG; hg += WS_THREADS / 32) {
     const int r0 = hg * M;
     const float l0 = lrun[r0], l1 = M > 1 ? lrun[r0 + 1] : 1.f;
@@ -303,11 +358,23 @@ __global__ void __launch_bounds__(WS_THREADS) attn_window_staged_kernel(WinArgs 
   }
 }
 
+// Key splits a row of the staged kernel can have: tiles of the kept tokens and of the window (or, without a window,
+// of all positions up to max_pos), WS_SPLIT_TILES a split. Floats of workspace for T rows (0: one split, none needed).
+HB_EXPORT int hb_attn_window_splits(int window, int keep_first, int max_pos) {
+  const int tiles = window > 0 ? min((window + KT - 1) / KT + 1 + (keep_first + KT - 1) / KT, max_pos / KT + 1) : max_pos / KT + 1;
+  return (tiles + WS_SPLIT_TILES - 1) / WS_SPLIT_TILES;
+}
+HB_EXPORT long hb_attn_window_workspace(int T, int H, int G, int E, int M, int window, int keep_first, int max_pos) {
+  const int sp = hb_attn_window_splits(window, keep_first, max_pos);
+  return sp <= 1 ? 0 : (long)T * G * sp * (H / G * M) * (E + 2);
+}
+
 HB_EXPORT int hb_attn_window(const void* q, int q_dt, const void* kc, const void* vc, int cache_dt, const int* bt,
                              int bt_stride, const int* row_req, const int* pos, const float* gate, long ld_gate,
                              int gate_off, void* out, int T, int H, int G, int D, int E, int M, int page_size, int window,
                              int keep_first, float scale, float lambda, float post, float eps, int norm, const int* q_len,
-                             int row_limit, int force_plain, cudaStream_t s) {
+                             int row_limit, int force_plain, float* part, long part_floats, int* arrived, int max_pos,
+                             cudaStream_t s) {
   if (T <= 0) return 0;
   if (G <= 0 || H % G) HB_FAIL("hb_attn_window: %d query heads are not a multiple of %d kv heads", H, G);
   if (M != 1 && M != 2) HB_FAIL("hb_attn_window: %d score maps (1 or 2)", M);
@@ -318,7 +385,7 @@ HB_EXPORT int hb_attn_window(const void* q, int q_dt, const void* kc, const void
   const size_t smem = ((size_t)R * (D + KT + E + 3) + KT) * sizeof(float);
   if (smem > 200 * 1024) HB_FAIL("hb_attn_window: %d score rows of %d + %d need %zu bytes of shared memory", R, D, E, smem);
   WinArgs A{q, kc, vc, bt, bt_stride, row_req, pos, gate, ld_gate, gate_off, out, H, G, D, E, M, page_size, window, keep_first,
-            scale, lambda, post, eps, norm, q_len, row_limit};
+            scale, lambda, post, eps, norm, q_len, row_limit, part, arrived, 1};
   const size_t staged = (size_t)2 * KT * (M * D + 8 + E) * 2 + ((size_t)R * (D + KT + E + 3)) * sizeof(float);
   if (q_dt == HB_BF16 && !force_plain && (M * D) % 8 == 0 && E % 8 == 0 && D % 8 == 0 && R <= 16 && staged <= 200 * 1024 &&
       !(((uintptr_t)kc | (uintptr_t)vc) & 15)) {
@@ -326,7 +393,11 @@ HB_EXPORT int hb_attn_window(const void* q, int q_dt, const void* kc, const void
       cudaError_t e = cudaFuncSetAttribute(attn_window_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged);
       if (e != cudaSuccess) HB_FAIL("hb_attn_window: %s", cudaGetErrorString(e));
     }
-    hb_launch(attn_window_staged_kernel, dim3(G, T), WS_THREADS, staged, s, A);
+    A.splits = hb_attn_window_splits(window, keep_first, max_pos);
+    if (A.splits > 1 && (!part || !arrived || part_floats < hb_attn_window_workspace(T, H, G, E, M, window, keep_first, max_pos)))
+      HB_FAIL("hb_attn_window: %d key splits a row need a workspace and counters", A.splits);
+    if (A.splits > 65535) HB_FAIL("hb_attn_window: %d key splits are beyond the grid limit", A.splits);
+    hb_launch(attn_window_staged_kernel, dim3(G, T, A.splits), WS_THREADS, staged, s, A);
     HB_CHECK_LAUNCH("hb_attn_window");
     return 0;
   }

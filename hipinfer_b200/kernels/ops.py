@@ -44,7 +44,7 @@ _SIGS = {
         "hb_delta_rule": [_p, _l, _i, _i, _i, _i, _i, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _f,
                           _i, _p],
         "hb_attn_window": [_p, _i, _p, _p, _i, _p, _i, _p, _p, _p, _l, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f,
-                           _f, _i, _p, _i, _i, _p],
+                           _f, _i, _p, _i, _i, _p, _l, _p, _i, _p],
         "hb_attn_window_flash": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f,
                                  _f, _f, _i, _p],
         "hb_attn_window_flash_supported": [_i, _i, _i, _i, _i],
@@ -271,11 +271,20 @@ def attention_window(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
               int(window), int(keep_first), float(scale), float(lam), float(post), float(eps), WINDOW_FLASH_MIN_ROWS, _stream())
         if min(batch.h_q_len) >= WINDOW_FLASH_MIN_ROWS:
             return out
+    # rows with many keys are split over several blocks, which meet in a workspace (bfloat16 rows kernel only)
+    lib = library.load("mixers")
+    lib.hb_attn_window_workspace.restype = C.c_long
+    max_pos = int(getattr(batch, "max_pos", 0)) or int(bt.shape[1]) * page_size - 1
+    n_ws = 0 if (q.dtype != torch.bfloat16 or force_plain) else lib.hb_attn_window_workspace(
+        T, n_heads, n_kv_heads, vdim, maps, int(window), int(keep_first), max_pos)
+    ws = torch.empty(n_ws, dtype=torch.float32, device=q.device) if n_ws else None
+    arrived = fast._decode_counters(q.device, T * n_kv_heads) if n_ws else None
     _call("mixers", "hb_attn_window", q.data_ptr(), _dt(q), k_cache.data_ptr(), v_cache.data_ptr(), _dt(k_cache),
           bt.data_ptr(), bt.stride(0), batch.row_request.data_ptr(), batch.positions.data_ptr(), _ptr(gate), gate_ld,
           int(gate_offset), out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim, maps, page_size, int(window), int(keep_first),
           float(scale), float(lam), float(post), float(eps), 1 if norm else 0,
-          batch.req_q_len.data_ptr() if flash else None, WINDOW_FLASH_MIN_ROWS, 1 if force_plain else 0, _stream())
+          batch.req_q_len.data_ptr() if flash else None, WINDOW_FLASH_MIN_ROWS, 1 if force_plain else 0, _ptr(ws), n_ws,
+          _ptr(arrived), max_pos, _stream())
     return out
 
 

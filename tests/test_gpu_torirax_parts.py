@@ -312,3 +312,18 @@ def test_row_kernels_with_and_without_shared_memory_tiles_give_the_same_bits(H, 
     a, _ = _attend(*args, seed=4)
     b, _ = _attend(*args, seed=4, force_plain=True)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("window, keep", [(700, 3), (None, 0), (300, 130)])
+def test_rows_whose_keys_are_split_over_several_blocks(window, keep):
+    """Windows of many key tiles: the bfloat16 rows kernel walks them in several blocks that meet in a workspace; planted
+    keys in the first, a middle and the last split and at the window's edge."""
+    n = 1500
+    rows = [1499, 900, 256, 255, 700, 40]
+    plant = [(0, 1499 - (window or 1500) + 1 if window else 0), (0, 1498), (1, 600), (4, 2)]
+    got, want = _attend(torch.bfloat16, 4, 2, 32, 64, 2, n, rows, window, keep, 16, plant=plant, seed=9)
+    close(got, want, torch.bfloat16)
+    plain_rows, _ = _attend(torch.bfloat16, 4, 2, 32, 64, 2, n, rows, window, keep, 16, plant=plant, seed=9, force_plain=True)
+    close(got, plain_rows.double().cpu(), torch.bfloat16, "split against one walk")
+    again, _ = _attend(torch.bfloat16, 4, 2, 32, 64, 2, n, rows, window, keep, 16, plant=plant, seed=9)
+    assert torch.equal(got, again)          # whichever block arrives last, the splits are joined in their order
