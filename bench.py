@@ -517,6 +517,7 @@ def design_bench(a) -> int:
            "prompt": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS, "window": a.window, "sizes": {}}
     clocks = ClockSampler().start()
     batches = [1, 8, 64]
+    clocks.__enter__()
     for name in a.sizes.split(","):
         size = dict(DESIGN_SIZES[name])
         if a.layers:
@@ -560,6 +561,7 @@ def design_bench(a) -> int:
             torch.cuda.empty_cache()
             res[which] = r
         out["sizes"][name] = dict(size, **res)
+    clocks.__exit__()
     out["clocks"] = clocks.summary()
     print(json.dumps(out))
     return 0

@@ -7,6 +7,10 @@ scripts/bench.py:126-212, and reports GB/s or TFLOP/s from algorithmic bytes and
     python -m hipinfer_b200.kernels.microbench attn_decode --batch 64 --context 2176
     python -m hipinfer_b200.kernels.microbench flash_prefill --tokens 2048
     python -m hipinfer_b200.kernels.microbench rmsnorm --m 2048 --n 2048
+    python -m hipinfer_b200.kernels.microbench delta_rule --tokens 2048 --batch 1 --heads 32 --head-dim 64
+    python -m hipinfer_b200.kernels.microbench attn_window --batch 8 --context 2048 --window 1024        (single rows)
+    python -m hipinfer_b200.kernels.microbench attn_window --tokens 2048 --window 1024                   (a prompt portion)
+    python -m hipinfer_b200.kernels.microbench layernorm|polynorm|scale_add --m 2048 --n 2048
 
 Between timed launches of kernels whose inputs fit in L2 a buffer larger than L2 is written
 (`--flush`, on by default) so that the figures are for operands coming from HBM.
@@ -56,7 +60,8 @@ def _prepared(fast, x, nw):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "rows_add", "rows_swiglu", "rows_qkv", "attn_decode", "flash_prefill", "flash_prefill_tc", "rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm_tc", "gemm_stream", "rows_add", "rows_swiglu", "rows_qkv", "attn_decode", "flash_prefill", "flash_prefill_tc", "rmsnorm",
+                                       "delta_rule", "attn_window", "layernorm", "polynorm", "scale_add"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -69,6 +74,8 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--window", type=int, default=1024, help="attn_window: the window (0: none); 4 first tokens are kept")
+    ap.add_argument("--value-dim", type=int, default=64, help="attn_window: width of a head's values (--head-dim: of one score map)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", dest="flush", action="store_false")
     ap.add_argument("--prepared-norm", action="store_true",
@@ -123,6 +130,61 @@ def main(argv=None) -> int:
         ms = timeit(fn, a.iters, a.flush)
         nbytes = N * K * 2 + M * K * 2 + c.numel() * c.element_size()
         out.update(M=M, N=N, K=K, epi=a.epi, ms=ms, tflops=2.0 * M * N * K / ms / 1e9, gbs=nbytes / ms / 1e6)
+    elif a.kernel in ("layernorm", "polynorm", "scale_add"):
+        x, w = rnd(a.m, a.n), torch.ones(a.n, device=dev, dtype=torch.bfloat16)
+        y = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+        if a.kernel == "layernorm":
+            fn, nbytes = (lambda: ops.layernorm(x, w, 1e-5, y)), a.m * a.n * 6
+        elif a.kernel == "polynorm":
+            fn, nbytes = (lambda: ops.polynorm(x, [1.0, 1.0, 1.0, 1.0], 1e-5, y)), a.m * a.n * 6
+        else:
+            x2 = rnd(a.m, a.n)
+            fn, nbytes = (lambda: ops.scale_add(x, x2, w)), a.m * a.n * 12
+        ms = timeit(fn, a.iters, a.flush)
+        out.update(M=a.m, H=a.n, ms=ms, gbs=nbytes / ms / 1e6)
+    elif a.kernel == "delta_rule":
+        from types import SimpleNamespace
+
+        T, R, Hh, D = a.tokens * a.batch if a.tokens < 16 else a.tokens, a.batch, a.heads, a.head_dim
+        n, HD = T // R, a.heads * a.head_dim
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        proj, w_raw = rnd(R * n, 5 * HD), rnd(R * n, HD)
+        vec = [rnd(HD).bfloat16() for _ in range(3)]
+        state, y = torch.zeros(R, Hh, D, D, device=dev), torch.empty(R * n, HD, device=dev, dtype=torch.bfloat16)
+        batch = SimpleNamespace(req_q_start=i32([i * n for i in range(R)]), req_q_len=i32([n] * R),
+                                req_state_slot=i32(list(range(R))), n_requests=R)
+        fn = lambda: ops.delta_rule(proj, (0, HD, 2 * HD, 3 * HD, 4 * HD), w_raw, *vec, state, batch, y, Hh, D, 0.6, 1e-6, 1e-5)
+        ms = timeit(fn, a.iters, a.flush)
+        nbytes = R * n * HD * (5 * 4 + 4 + 2) + 2 * R * Hh * D * D * 4
+        out.update(requests=R, tokens_each=n, heads=Hh, head_dim=D, ms=ms, us_per_token=ms * 1e3 / n, gbs=nbytes / ms / 1e6)
+    elif a.kernel == "attn_window":
+        from types import SimpleNamespace
+
+        H, G, D, E, ps, window = a.heads, a.kv_heads, a.head_dim, a.value_dim, a.page_size, a.window
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        rows = a.tokens >= 16                                  # a portion of --tokens rows, else --batch single rows at --context
+        R, T, ctx = (1, a.tokens, a.tokens) if rows else (a.batch, a.batch, a.context)
+        pages = ctx // ps + 1
+        kc, vc = rnd(R * pages, G, ps, 2 * D).bfloat16(), rnd(R * pages, G, ps, E).bfloat16()
+        bt = torch.arange(R * pages, dtype=torch.int32, device=dev).view(R, pages)
+        q, gate, y = rnd(T, H * 2 * D).bfloat16(), rnd(T, H * E), torch.empty(T, H * E, device=dev, dtype=torch.bfloat16)
+        if rows:
+            batch = SimpleNamespace(block_tables=[bt], row_request=i32([0] * T), positions=i32(list(range(T))), max_q_len=T,
+                                    n_requests=1, req_q_start=i32([0]), req_q_len=i32([T]), req_ctx_len=i32([0]), h_q_len=[T],
+                                    max_pos=T - 1)
+            pairs = sum(min(p + 1, window + 4) if window else p + 1 for p in range(T))
+        else:
+            batch = SimpleNamespace(block_tables=[bt], row_request=i32(list(range(R))), positions=i32([ctx] * R), max_q_len=1,
+                                    max_pos=ctx)
+            pairs = R * (min(ctx + 1, window + 4) if window else ctx + 1)
+        fn = lambda: ops.attention_window(q, kc, vc, batch, 0, y, H, G, D, E, 2, ps, window, 4, D ** -0.5, 0.5, 0.5, 1e-5, True,
+                                          gate=gate)
+        ms = timeit(fn, a.iters, a.flush)
+        nbytes = (pairs if not rows else min(ctx, ctx)) * G * (2 * D + E) * 2
+        out.update(rows=T, requests=R, heads=H, kv_heads=G, map_dim=D, value_dim=E, window=window, ms=ms,
+                   tflops=pairs * H * (4 * D + 4 * E) / ms / 1e9)
+        if not rows:
+            out.update(gbs=nbytes / ms / 1e6)
     elif a.kernel == "rmsnorm":
         x, w = rnd(a.m, a.n), torch.ones(a.n, device=dev, dtype=torch.bfloat16)
         y = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
