@@ -314,13 +314,28 @@ __global__ void __launch_bounds__(WS_THREADS) attn_window_staged_kernel(WinArgs 
     if (!last) return;
     __threadfence();
     const float* all = A.part + slot * R * (E + 2);
+    // (the splits' values are asked for eight at a time: one trip to L2 for eight splits, not one a split)
+    const size_t zs = (size_t)R * (E + 2);
     if (tid < R) {
+      const float* pm = all + (size_t)tid * (E + 2) + E;
       float m = -INFINITY;
-      for (int z = 0; z < n_splits; z++) m = fmaxf(m, __ldcg(all + ((size_t)z * R + tid) * (E + 2) + E));
+      for (int z0 = 0; z0 < n_splits; z0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) v[k] = z0 + k < n_splits ? __ldcg(pm + (z0 + k) * zs) : -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 8; k++) m = fmaxf(m, v[k]);
+      }
       float l = 0.f;
-      for (int z = 0; z < n_splits; z++) {
-        const float* pz = all + ((size_t)z * R + tid) * (E + 2);
-        l = fmaf(__ldcg(pz + E + 1), expf(__ldcg(pz + E) - m), l);
+      for (int z0 = 0; z0 < n_splits; z0 += 8) {
+        float v[8], w[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          v[k] = z0 + k < n_splits ? __ldcg(pm + (z0 + k) * zs) : -INFINITY;
+          w[k] = z0 + k < n_splits ? __ldcg(pm + 1 + (z0 + k) * zs) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) l = fmaf(w[k], expf(v[k] - m), l);
       }
       mrun[tid] = m;
       lrun[tid] = l;
@@ -328,10 +343,18 @@ __global__ void __launch_bounds__(WS_THREADS) attn_window_staged_kernel(WinArgs 
     __syncthreads();
     for (int i = tid; i < R * E; i += WS_THREADS) {
       const int r = i / E, e = i - r * E;
+      const float* pe = all + (size_t)r * (E + 2);
+      const float m = mrun[r];
       float a = 0.f;
-      for (int z = 0; z < n_splits; z++) {
-        const float* pz = all + ((size_t)z * R + r) * (E + 2);
-        a = fmaf(__ldcg(pz + e), expf(__ldcg(pz + E) - mrun[r]), a);
+      for (int z0 = 0; z0 < n_splits; z0 += 8) {
+        float v[8], w[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          v[k] = z0 + k < n_splits ? __ldcg(pe + e + (z0 + k) * zs) : 0.f;
+          w[k] = z0 + k < n_splits ? __ldcg(pe + E + (z0 + k) * zs) : -INFINITY;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) a = fmaf(v[k], expf(w[k] - m), a);
       }
       acc[i] = a;
     }

@@ -48,6 +48,9 @@ _SIGS = {
         "hb_attn_window_flash": [_p, _p, _p, _p, _i, _p, _p, _p, _p, _l, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f,
                                  _f, _f, _i, _p],
         "hb_attn_window_flash_supported": [_i, _i, _i, _i, _i],
+        "hb_attn_window_rows_mma_supported": [_i, _i, _i, _i, _i],
+        "hb_attn_window_rows_mma": [_p, _p, _p, _p, _i, _p, _p, _p, _l, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f, _f,
+                                    _p, _i, _p, _l, _p, _i, _p],
     },
 }
 _fn_cache = {}
@@ -241,7 +244,8 @@ WINDOW_FLASH_MIN_ROWS = 16     # requests that bring at least this many rows go 
 def attention_window(q, k_cache, v_cache, batch, group: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
                      maps: int, page_size: int, window: int, keep_first: int, scale: float, lam: float = 0.0,
                      post: float = 1.0, eps: float = 0.0, norm: bool = False, gate: Optional[torch.Tensor] = None,
-                     gate_offset: int = 0, force_rows: bool = False, force_plain: bool = False) -> torch.Tensor:
+                     gate_offset: int = 0, force_rows: bool = False, force_plain: bool = False,
+                     force_simt: bool = False) -> torch.Tensor:
     """Attention of the step's rows over their requests' pages with a window that keeps the first tokens, `maps` score
     maps per head (2: out = a0 - lam * a1), keys `dim` and values `vdim` wide, the head's result optionally divided by
     its root mean square and times `post`, and times sigmoid(gate[:, gate_offset + ...]) (float32) where a gate is given
@@ -271,10 +275,24 @@ def attention_window(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
               int(window), int(keep_first), float(scale), float(lam), float(post), float(eps), WINDOW_FLASH_MIN_ROWS, _stream())
         if min(batch.h_q_len) >= WINDOW_FLASH_MIN_ROWS:
             return out
-    # rows with many keys are split over several blocks, which meet in a workspace (bfloat16 rows kernel only)
+    # rows with many keys are split over several blocks, which meet in a workspace (bfloat16 rows kernels only)
     lib = library.load("mixers")
     lib.hb_attn_window_workspace.restype = C.c_long
+    lib.hb_attn_window_rows_mma_workspace.restype = C.c_long
     max_pos = int(getattr(batch, "max_pos", 0)) or int(bt.shape[1]) * page_size - 1
+    q_len_ptr = batch.req_q_len.data_ptr() if flash else None
+    if (maps == 2 and norm and q.dtype == torch.bfloat16 and not fast.PLAIN_ONLY and not force_plain and not force_simt
+            and _fn("mixers", "hb_attn_window_rows_mma_supported")(n_heads, n_kv_heads, dim, vdim, maps) == 1):
+        # the heads of a kv head as the rows of a warp MMA tile
+        n_ws = lib.hb_attn_window_rows_mma_workspace(T, n_heads, n_kv_heads, vdim, int(window), int(keep_first), max_pos)
+        ws = torch.empty(n_ws, dtype=torch.float32, device=q.device) if n_ws else None
+        arrived = fast._decode_counters(q.device, T * n_kv_heads) if n_ws else None
+        _call("mixers", "hb_attn_window_rows_mma", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), bt.data_ptr(),
+              bt.stride(0), batch.row_request.data_ptr(), batch.positions.data_ptr(), _ptr(gate), gate_ld, int(gate_offset),
+              out.data_ptr(), T, n_heads, n_kv_heads, dim, vdim, page_size, int(window), int(keep_first), float(scale),
+              float(lam), float(post), float(eps), q_len_ptr, WINDOW_FLASH_MIN_ROWS, _ptr(ws), n_ws, _ptr(arrived), max_pos,
+              _stream())
+        return out
     n_ws = 0 if (q.dtype != torch.bfloat16 or force_plain) else lib.hb_attn_window_workspace(
         T, n_heads, n_kv_heads, vdim, maps, int(window), int(keep_first), max_pos)
     ws = torch.empty(n_ws, dtype=torch.float32, device=q.device) if n_ws else None

@@ -205,7 +205,7 @@ def _paged(k, v, G, ps, seed):
 
 
 def _attend(dtype, H, G, D, E, M, n_keys, q_pos, window, keep, ps, plant=(), lam=0.7, c=0.4, gate=True, seed=0, drop_dead=True,
-            portion=False, force_plain=False):
+            portion=False, force_plain=False, force_simt=False):
     """Rows at positions q_pos over n_keys keys; `plant`: (row, key position) whose score is made to stand out in BOTH maps.
     Pages that no row can see are taken out of the block table (-1), as the cache manager does. Returns (got, want)."""
     from hipinfer_b200.kernels import ops
@@ -235,7 +235,7 @@ def _attend(dtype, H, G, D, E, M, n_keys, q_pos, window, keep, ps, plant=(), lam
     scale = 1.0 / math.sqrt(D)
     ops.attention_window(q.reshape(T, -1).to(DEV), kc.to(DEV), vc.to(DEV), batch, 0, out, H, G, D, E, M, ps, window or 0, keep,
                          scale, lam, 1.0 - c, 1e-5, M == 2, gate=g_raw.to(DEV) if gate else None, gate_offset=5,
-                         force_plain=force_plain)
+                         force_plain=force_plain, force_simt=force_simt)
     qd, kd, vd = q.double(), k.double(), v.double()
     want = torch.zeros(T, H, E, dtype=torch.float64)
     for t, p in enumerate(q_pos):
@@ -309,7 +309,7 @@ def test_window_attention_portions_on_tensor_cores(D, E, window, keep, ctx, n):
 @pytest.mark.parametrize("H, G, D, E, M", [(4, 2, 16, 24, 2), (8, 2, 32, 64, 2), (4, 1, 64, 128, 2), (2, 1, 40, 16, 1)])
 def test_row_kernels_with_and_without_shared_memory_tiles_give_the_same_bits(H, G, D, E, M):
     args = (torch.bfloat16, H, G, D, E, M, 300, [0, 5, 63, 64, 200, 299], 90, 3, 16)
-    a, _ = _attend(*args, seed=4)
+    a, _ = _attend(*args, seed=4, force_simt=True)
     b, _ = _attend(*args, seed=4, force_plain=True)
     assert torch.equal(a, b)
 
@@ -327,3 +327,20 @@ def test_rows_whose_keys_are_split_over_several_blocks(window, keep):
     close(got, plain_rows.double().cpu(), torch.bfloat16, "split against one walk")
     again, _ = _attend(torch.bfloat16, 4, 2, 32, 64, 2, n, rows, window, keep, 16, plant=plant, seed=9)
     assert torch.equal(got, again)          # whichever block arrives last, the splits are joined in their order
+    simt, _ = _attend(torch.bfloat16, 4, 2, 32, 64, 2, n, rows, window, keep, 16, plant=plant, seed=9, force_simt=True)
+    close(simt, want, torch.bfloat16, "the kernel without warp MMAs")
+    close(got, simt.double().cpu(), torch.bfloat16, "warp MMAs against FFMA")
+
+
+@pytest.mark.parametrize("H, G, D, E", [(4, 1, 32, 64), (16, 1, 64, 128), (32, 8, 32, 64), (3, 3, 128, 64), (12, 2, 64, 64),
+                                        (5, 1, 32, 128), (2, 1, 128, 128)])
+@pytest.mark.parametrize("window, keep", [(100, 2), (None, 0), (64, 64), (1, 1)])
+def test_single_rows_on_warp_mmas(H, G, D, E, window, keep):
+    """Groups of 1 to 16 heads as the rows of an MMA tile, every size the kernel takes; rows at the first positions, at tile
+    and page borders and far out; planted keys at the window's edge and among the kept tokens."""
+    rows = [0, 1, 15, 16, 63, 64, 65, 500, 999]
+    plant = [(7, 500 - window + 1), (8, 999 - window)] if window and window > 1 else [(7, 3)]
+    if keep:
+        plant.append((8, keep - 1))
+    got, want = _attend(torch.bfloat16, H, G, D, E, 2, 1000, rows, window, keep, 16, plant=plant, seed=H + D)
+    close(got, want, torch.bfloat16)

@@ -139,3 +139,32 @@ def test_plain_mask_edges():
     assert abs(float(p[2].sum()) - 1) < 1e-12 and float(p[2, 19]) == 0 and float(p[2, 20]) > 0
     lam = plain.differential_lambda(torch.ones(4) * 0.5, torch.ones(4), torch.zeros(4), torch.ones(4), 0.25)
     assert abs(lam - (math.exp(2.0) - 1 + 0.25)) < 1e-12
+
+
+def test_random_model_from_the_command_line_and_back(tmp_path):
+    """`random-model` writes a Torirax folder whose config reads back equal and whose tensors fit the model's list (the
+    rank the file decides takes the spec's default)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from hipinfer_b200.config import load_config
+    from hipinfer_b200.weights.safetensors_io import ModelFiles
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(tm.R))
+    out = tmp_path / "model"
+    r = subprocess.run([sys.executable, "-m", "hipinfer_b200", "random-model", "--config", str(cfg), "--out", str(out), "--seed", "3"],
+                       capture_output=True, text=True, cwd=root, env=dict(os.environ, PYTHONPATH=root))
+    assert r.returncode == 0, r.stderr[-2000:]
+    c = load_config(str(out))
+    assert c == config_from_dict(tm.R)
+    spec = get_architecture(c.architecture).build_spec(c)
+    f = ModelFiles(str(out))
+    try:
+        check_names(str(out), spec_param_specs(spec), {n: f.info(n)[1] for n in f.names()}, [], {n: f.info(n)[0] for n in f.names()})
+        assert f.info("l0.mix.w1")[1] == (16, 128) and f.info("l2.mix.w1")[1] == (24, 128)
+    finally:
+        f.close()
