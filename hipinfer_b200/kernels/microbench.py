@@ -9,7 +9,7 @@ scripts/bench.py:126-212, and reports GB/s or TFLOP/s from algorithmic bytes and
     python -m hipinfer_b200.kernels.microbench rmsnorm --m 2048 --n 2048
     python -m hipinfer_b200.kernels.microbench delta_rule --tokens 2048 --batch 1 --heads 32 --head-dim 64
     python -m hipinfer_b200.kernels.microbench attn_window --batch 8 --context 2048 --window 1024        (single rows)
-    python -m hipinfer_b200.kernels.microbench attn_window --tokens 2048 --window 1024                   (a prompt portion)
+    python -m hipinfer_b200.kernels.microbench attn_window --portion --tokens 2048 --window 1024         (a prompt portion)
     python -m hipinfer_b200.kernels.microbench layernorm|polynorm|scale_add --m 2048 --n 2048
 
 Between timed launches of kernels whose inputs fit in L2 a buffer larger than L2 is written
@@ -75,7 +75,8 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--window", type=int, default=1024, help="attn_window: the window (0: none); 4 first tokens are kept")
-    ap.add_argument("--value-dim", type=int, default=64, help="attn_window: width of a head's values (--head-dim: of one score map)")
+    ap.add_argument("--value-dim", type=int, default=64, help="attn_window: width of a head's values (a score map is --head-dim / 2 wide)")
+    ap.add_argument("--portion", action="store_true", help="attn_window: one request's portion of --tokens rows instead of --batch single rows")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", dest="flush", action="store_false")
     ap.add_argument("--prepared-norm", action="store_true",
@@ -160,9 +161,9 @@ def main(argv=None) -> int:
     elif a.kernel == "attn_window":
         from types import SimpleNamespace
 
-        H, G, D, E, ps, window = a.heads, a.kv_heads, a.head_dim, a.value_dim, a.page_size, a.window
+        H, G, D, E, ps, window = a.heads, a.kv_heads, a.head_dim // 2, a.value_dim, a.page_size, a.window
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
-        rows = a.tokens >= 16                                  # a portion of --tokens rows, else --batch single rows at --context
+        rows = a.portion                                       # a portion of --tokens rows, else --batch single rows at --context
         R, T, ctx = (1, a.tokens, a.tokens) if rows else (a.batch, a.batch, a.context)
         pages = ctx // ps + 1
         kc, vc = rnd(R * pages, G, ps, 2 * D).bfloat16(), rnd(R * pages, G, ps, E).bfloat16()
@@ -180,7 +181,7 @@ def main(argv=None) -> int:
         fn = lambda: ops.attention_window(q, kc, vc, batch, 0, y, H, G, D, E, 2, ps, window, 4, D ** -0.5, 0.5, 0.5, 1e-5, True,
                                           gate=gate)
         ms = timeit(fn, a.iters, a.flush)
-        nbytes = (pairs if not rows else min(ctx, ctx)) * G * (2 * D + E) * 2
+        nbytes = pairs * G * (2 * D + E) * 2                   # single rows: every visible key and value once a kv head
         out.update(rows=T, requests=R, heads=H, kv_heads=G, map_dim=D, value_dim=E, window=window, ms=ms,
                    tflops=pairs * H * (4 * D + 4 * E) / ms / 1e9)
         if not rows:
