@@ -489,7 +489,7 @@ def kernel_table(one, reps: int = 3):
         for lib in libs:
             lib.hb_set_pdl(1)
     with tempfile.TemporaryDirectory() as tmp:
-        path = os.path.join(tmp, "trace.json")
+        path = os.path.join(tmp, "kernels.json")
         prof.export_chrome_trace(path)
         with open(path) as f:
             events = sorted((e for e in _json.load(f)["traceEvents"] if e.get("cat") == "kernel"), key=lambda e: e["ts"])

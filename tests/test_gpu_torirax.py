@@ -10,7 +10,8 @@ import torirax_models as tm
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"p": [1, 2, 5, 40, 90, 130, 33, 64], "q": [3, 1, 70, 16, 17, 100, 48, 2], "r": [300, 7, 129, 64, 200, 65, 1, 150]}
+LENGTHS = {"p": [1, 2, 5, 40, 90, 130, 33, 64], "q": [3, 1, 70, 16, 17, 100, 48, 2], "r": [300, 7, 129, 64, 200, 65, 1, 150],
+           "s": [420, 31, 257, 2, 64, 90, 16, 300]}
 TOL = {"float32": 3e-5, "bfloat16": 2.5e-2}
 
 
@@ -23,7 +24,7 @@ def _close(got, ref, dtype, what):
                              f"{int((bad > TOL[dtype] * scale).nonzero()[0])} of {got.shape[0]}")
 
 
-@pytest.fixture(scope="module", params=[(m, d) for m in ("p", "q", "r") for d in ("float32", "bfloat16")], ids=lambda p: f"{p[0]}-{p[1]}")
+@pytest.fixture(scope="module", params=[(m, d) for m in ("p", "q", "r", "s") for d in ("float32", "bfloat16")], ids=lambda p: f"{p[0]}-{p[1]}")
 def setup(request, tmp_path_factory):
     from hipinfer_b200.engine.runner import ModelRunner
 

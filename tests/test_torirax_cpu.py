@@ -78,6 +78,12 @@ def test_cache_plan_shares_and_retains_the_widest_look_back():
     assert g.kind == "window_keep_first" and g.window == 130 and dict(g.extra)["keep_first"] == 5      # the reader's, wider
     assert g.planes == (("k", 2, 64), ("v", 2, 64))
     assert [o.reads_cache_of for o in spec.order] == [None, None, None, 1, None]
+    # a reader without a window: the cache it reads keeps everything, the other cache of the same shape keeps its window
+    c, spec = _spec(tm.S)
+    m = DecoderModel(spec, BuildContext.meta())
+    kinds = {g.kind: g for g in m.cache_groups}
+    assert m.cache_groups[m.cache_plan[1].group].kind == "full" and m.cache_plan[4].group == m.cache_plan[1].group
+    assert m.cache_groups[m.cache_plan[3].group].kind == "window_keep_first" and kinds["window_keep_first"].window == 50
     # no window anywhere: everything is kept
     c, spec = _spec(tm.Q)
     m = DecoderModel(spec, BuildContext.meta())

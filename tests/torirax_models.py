@@ -45,7 +45,14 @@ R = model(211, 128, [delta(2, 64), attn(8, 2, 32, 64, window=70, keep=2, ff=192)
                      attn(8, 2, 32, 64, window=130, keep=5, kv_from=1), attn(4, 4, 16, 16, window=64, keep=64, ff=64)],
           max_positions=700, scale=3.0)
 
-MODELS = {"p": P, "q": Q, "r": R}
+# S: delta heads wider together than the model (3 x 64 over a width of 96) and narrower (1 x 32); every attention head its
+#    own kv head with maps of 64 and values of 128 (tensor-core kernels with one head a group); no kept tokens; a second
+#    cache of the same shape with another window; a reader WITHOUT a window, so the cache it reads keeps everything
+S = model(131, 96, [delta(3, 64), attn(4, 4, 64, 128, window=200, keep=0, ff=160, diff=0.1), delta(1, 32, ff=40),
+                    attn(4, 4, 64, 128, window=50, keep=7), attn(4, 4, 64, 128, kv_from=1, diff=0.9)],
+          max_positions=450, scale=1.5, eps=1e-5)
+
+MODELS = {"p": P, "q": Q, "r": R, "s": S}
 
 
 def draw_weights(config: dict, seed: int, dtype=torch.bfloat16):
