@@ -183,3 +183,34 @@ def test_greedy_generation_through_the_entry_point_and_scheduler(setup):
             same(done[rid], want[i][0], want[i][1], f"scheduler request {i}")
     finally:
         eng.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("layers", ["delta only", "attention only", "one layer", "odd sizes"])
+def test_models_of_one_kind_of_layer(layers, dtype, tmp_path):
+    """A model without any cache (recurrent layers only), one without any state (attention only, the second layer reading
+    the first one's cache), a single layer, and sizes no fast kernel takes: whole, in portions and token by token."""
+    from hipinfer_b200.engine.runner import ModelRunner
+
+    if layers == "odd sizes":       # a width that is no multiple of 4, heads of 20 and 10, values of 6: nothing vectorised applies
+        cfg = tm.model(90, 50, [tm.delta(1, 20, ff=30, rank=3), tm.attn(3, 1, 10, 6, window=5, keep=1, ff=22)], max_positions=200)
+    else:
+        cfg = tm.model(90, 64, {"delta only": [tm.delta(2, 32, ff=48), tm.delta(4, 16)],
+                                "attention only": [tm.attn(2, 1, 32, 64, window=30, keep=2, ff=48),
+                                                   tm.attn(2, 1, 32, 64, window=12, keep=1, kv_from=0)],
+                                "one layer": [tm.attn(4, 4, 16, 16, ff=32)]}[layers], max_positions=200)
+    folder, cfg, w = tm.make_folder(tmp_path / "m", cfg, seed=3, dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+    reqs = {"a": tiny.random_tokens(150, 90, 1), "b": tiny.random_tokens(37, 90, 2)}
+    model = plain.PlainTorirax(cfg, w)
+    ref = {}
+    for rid, toks in reqs.items():
+        model.reset()
+        ref[rid] = model.forward(toks)
+    runner = ModelRunner.from_folder(folder, dtype=dtype, page_size=16, num_pages=24, max_num_seqs=2)
+    st = tiny.RunnerStepper(runner)
+    for plan in (tiny.plan_whole(reqs), tiny.plan_portions(reqs, (5, 2, 40, 1, 17)), tiny.plan_tail_decode(reqs, 20),
+                 tiny.plan_mixed(reqs, 4, max_live=2)):
+        got = tiny.run_plan(st, reqs, plan)
+        for rid in reqs:
+            _close(got[rid], ref[rid], dtype, f"{layers} {rid}")
+    assert not runner.live_requests()
