@@ -79,3 +79,26 @@ def test_generate_prints_the_plain_tokens(tmp_path, which, mode, via_module):
                 assert float(top[0] - top[1]) < 0.02 * float(steps[i].abs().max()), (i, got, want)
                 break
         assert len(got) == len(want)
+
+
+@pytest.mark.gpu
+def test_generate_serves_the_second_architecture(tmp_path):
+    """The same command on a Torirax folder (config.json names the architecture as a plain string): prompt portions of 8
+    tokens through the scheduler, then greedy decoding, in 32-bit against the plain implementation."""
+    import plain_torirax
+    import torirax_models as tm
+
+    folder, cfg, w = tm.make_folder(tmp_path / "model", "p", seed=5, dtype=torch.float32)
+    prompt = tiny.random_tokens(29, cfg["vocab"], 8)
+    model = plain_torirax.PlainTorirax(cfg, w)
+    logits, want = model.forward(prompt)[-1], []
+    for _ in range(6):
+        want.append(int(logits.argmax()))
+        logits = model.forward([want[-1]])[-1]
+    r = run([sys.executable, "-m", "hipinfer_b200", "generate", "--model", folder, "--tokens", *map(str, prompt), "--new", "6",
+             "--mode", "fp32", "--max-seq", "64", "--max-batch", "2", "--max-prefill", "8"])
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = r.stdout.strip().splitlines()
+    shape = ast.literal_eval(lines[-2])
+    assert shape["vocab"] == cfg["vocab"] and shape["hidden"] == cfg["width"] and shape["layers"] == len(cfg["layers"])
+    assert ast.literal_eval(lines[-1]) == want
