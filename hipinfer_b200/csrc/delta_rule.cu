@@ -116,7 +116,7 @@ __global__ void delta_rule_any_kernel(DeltaArgs A) {
 constexpr int DR_CH = 16;
 
 template <typename TW, typename TO, int NR, int TPC>
-__global__ void __launch_bounds__(NR * TPC * TPC) delta_rule_kernel(DeltaArgs A) {
+__global__ void __launch_bounds__(NR * TPC * TPC, (NR * TPC * TPC <= 256 ? 2 : 1)) delta_rule_kernel(DeltaArgs A) {
   constexpr int D = NR * TPC, NT = D * TPC, NW = NT / 32, TPW = DR_CH / NW, CPL = D / 32;
   static_assert(TPW >= 1 && TPW * NW == DR_CH && CPL >= 1 && NR % 4 == 0, "chunk, warps and head size must fit");
   extern __shared__ __align__(16) float dr_smem[];
@@ -143,6 +143,25 @@ __global__ void __launch_bounds__(NR * TPC * TPC) delta_rule_kernel(DeltaArgs A)
 
   // raw values of a chunk's tokens: warp `warp` takes tokens warp, warp + NW, ..; a lane channels lane, lane + 32, ..
   float pre[TPW][CPL][5];              // k, r, v, a_raw, w_raw
+  float gate[TPW][CPL];                // the gate's raw values of the chunk being walked (asked for before the walk)
+  float cab[CPL], cwb[CPL], cnw[CPL];  // this lane's channels of the two biases and the norm weight
+#pragma unroll
+  for (int y = 0; y < CPL; y++) {
+    cab[y] = hb_to_float(ab[hc + lane + 32 * y]);
+    cwb[y] = hb_to_float(wb[hc + lane + 32 * y]);
+    cnw[y] = hb_to_float(nwt[hc + lane + 32 * y]);
+  }
+  auto fetch_gate = [&](int base) {
+#pragma unroll
+    for (int x = 0; x < TPW; x++) {
+      const int tt = warp + x * NW;
+      if (base + tt < n) {
+        const float* row = A.proj + (size_t)(t0 + base + tt) * A.ld;
+#pragma unroll
+        for (int y = 0; y < CPL; y++) gate[x][y] = row[A.g_off + hc + lane + 32 * y];
+      }
+    }
+  };
   auto fetch = [&](int base) {
 #pragma unroll
     for (int x = 0; x < TPW; x++) {
@@ -176,19 +195,20 @@ __global__ void __launch_bounds__(NR * TPC * TPC) delta_rule_kernel(DeltaArgs A)
         const float inv = 1.f / sqrtf(kk + A.unit_eps);
 #pragma unroll
         for (int y = 0; y < CPL; y++) {
-          const int cl = lane + 32 * y, c = hc + cl;
+          const int cl = lane + 32 * y;
           const float kj = pre[x][y][0], uj = kj * inv;
           vk[tt * D + cl] = kj;
           vu[tt * D + cl] = uj;
           vr[tt * D + cl] = pre[x][y][1];
           vv[tt * D + cl] = pre[x][y][2];
-          vau[tt * D + cl] = sigmoidf_(pre[x][y][3] + hb_to_float(ab[c])) * uj;
-          vw[tt * D + cl] = expf(-A.decay_scale * sigmoidf_(pre[x][y][4] + hb_to_float(wb[c])));
+          vau[tt * D + cl] = sigmoidf_(pre[x][y][3] + cab[y]) * uj;
+          vw[tt * D + cl] = expf(-A.decay_scale * sigmoidf_(pre[x][y][4] + cwb[y]));
         }
       }
     }
     __syncthreads();
-    if (base + DR_CH < n) fetch(base + DR_CH);               // in flight during the walk
+    fetch_gate(base);                                        // both in flight during the walk
+    if (base + DR_CH < n) fetch(base + DR_CH);
     const int m = min(DR_CH, n - base);
     for (int tt = 0; tt < m; tt++) {
       // (heads of up to 64) all of the token's vectors are asked for at once: one wait for shared memory a token
@@ -245,11 +265,10 @@ __global__ void __launch_bounds__(NR * TPC * TPC) delta_rule_kernel(DeltaArgs A)
         oo = hb_warp_sum(oo);
         const float f = rsqrtf(oo / (float)D + A.eps);
         const size_t t = (size_t)(t0 + base + tt);
-        const float* row = A.proj + t * A.ld;
 #pragma unroll
         for (int y = 0; y < CPL; y++) {
           const int c = hc + lane + 32 * y;
-          ((TO*)A.out)[t * A.heads * D + c] = hb_from_float<TO>(ov[y] * f * hb_to_float(nwt[c]) * sigmoidf_(row[A.g_off + c]));
+          ((TO*)A.out)[t * A.heads * D + c] = hb_from_float<TO>(ov[y] * f * cnw[y] * sigmoidf_(gate[x][y]));
         }
       }
     }
