@@ -70,6 +70,10 @@ def ensure_built(verbose: bool = True) -> str:
     if not os.path.isdir(REF_SRC):
         raise ReferenceUnavailable(f"no checkout of the reference at {REF_SRC} (HIPINFER_REFERENCE_SRC) and no built "
                                    f"library at {so}")
+    absent = [rel for rel in COPIED if not os.path.isfile(os.path.join(REF_SRC, rel))]
+    if absent:
+        raise ReferenceUnavailable(f"the checkout of the reference at {REF_SRC} lacks {', '.join(absent)} and there is no built "
+                                   f"library at {so}")
     for rel in COPIED:
         dst = os.path.join(REF_DIR, rel)
         os.makedirs(os.path.dirname(dst), exist_ok=True)
