@@ -2,7 +2,10 @@ from .base import (Architecture, ConfigError, ModelConfig, config_from_dict, get
                    register_architecture, registered_architectures, save_config, take)
 from .llama import Llama3RopeScaling, LlamaConfig
 from .torirax import DeltaMixerConfig, DiffAttentionConfig, ToriraxConfig, ToriraxLayerConfig
+from .vegodra import (ChunkedAttentionConfig, GlaConfig, LatentAttentionConfig, RotaryConfig, VegodraConfig,
+                      VegodraLayerConfig)
 
 __all__ = ["Architecture", "ConfigError", "ModelConfig", "config_from_dict", "get_architecture", "load_config",
            "register_architecture", "registered_architectures", "save_config", "take", "Llama3RopeScaling",
-           "LlamaConfig", "DeltaMixerConfig", "DiffAttentionConfig", "ToriraxConfig", "ToriraxLayerConfig"]
+           "LlamaConfig", "DeltaMixerConfig", "DiffAttentionConfig", "ToriraxConfig", "ToriraxLayerConfig",
+           "ChunkedAttentionConfig", "GlaConfig", "LatentAttentionConfig", "RotaryConfig", "VegodraConfig", "VegodraLayerConfig"]

@@ -143,12 +143,13 @@ HB_EXPORT int hb_embed_pos(const void* table, const void* ptab, int table_dt, co
 }
 
 // ---------------------------------------------------------------------------------------
-// Layer norm with a weight and no bias: y = w * (x - mean) / sqrt(mean((x - mean)^2) + eps). Two sums in 32-bit
-// (the mean first, then the squared deviations from it), the result rounded once. `rows` as in RMSNorm.
+// Layer norm with a weight and an optional bias: y = w * (x - mean) / sqrt(mean((x - mean)^2) + eps) (+ b). Two sums in
+// 32-bit (the mean first, then the squared deviations from it), the result rounded once. `rows` as in RMSNorm.
 // ---------------------------------------------------------------------------------------
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
-                                                        TO* __restrict__ y, const int* __restrict__ rows, int H, float eps) {
+                                                        const TW* __restrict__ b, TO* __restrict__ y,
+                                                        const int* __restrict__ rows, int H, float eps) {
   __shared__ float sh[32];
   hb_pdl_launch();
   hb_pdl_wait();
@@ -164,14 +165,17 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict_
   }
   const float inv = rsqrtf(hb_block_sum(ss, sh) / (float)H + eps);
   TO* yr = y + (size_t)blockIdx.x * H;
-  for (int i = threadIdx.x; i < H; i += 256) yr[i] = hb_from_float<TO>(hb_to_float(w[i]) * ((xr[i] - mean) * inv));
+  for (int i = threadIdx.x; i < H; i += 256) {
+    const float v = hb_to_float(w[i]) * ((xr[i] - mean) * inv);
+    yr[i] = hb_from_float<TO>(b ? v + hb_to_float(b[i]) : v);
+  }
 }
 
 // The same with the row in registers (H a multiple of 4, at most 256 * 4 * NV elements): one read of x.
 template <typename TW, typename TO, int NV>
 __global__ void __launch_bounds__(256) layernorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w,
-                                                            TO* __restrict__ y, const int* __restrict__ rows, int H,
-                                                            float eps) {
+                                                            const TW* __restrict__ b, TO* __restrict__ y,
+                                                            const int* __restrict__ rows, int H, float eps) {
   __shared__ float sh[32];
   hb_pdl_launch();
   hb_pdl_wait();
@@ -204,27 +208,31 @@ __global__ void __launch_bounds__(256) layernorm_vec_kernel(const float* __restr
     const int c = threadIdx.x + i * 256;
     if (c < nvec) {
       const float4 ww = hb_load4(w + 4 * c);
-      hb_store4(yr + 4 * c, make_float4(ww.x * (v[i].x * inv), ww.y * (v[i].y * inv), ww.z * (v[i].z * inv),
-                                        ww.w * (v[i].w * inv)));
+      float4 o = make_float4(ww.x * (v[i].x * inv), ww.y * (v[i].y * inv), ww.z * (v[i].z * inv), ww.w * (v[i].w * inv));
+      if (b) {
+        const float4 bb = hb_load4(b + 4 * c);
+        o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+      }
+      hb_store4(yr + 4 * c, o);
     }
   }
 }
 
-HB_EXPORT int hb_layernorm(const float* x, const void* w, int w_dt, void* y, int y_dt, const int* rows, int M, int H,
-                           float eps, cudaStream_t s) {
+HB_EXPORT int hb_layernorm(const float* x, const void* w, const void* b, int w_dt, void* y, int y_dt, const int* rows, int M,
+                           int H, float eps, cudaStream_t s) {
   if (M <= 0) return 0;
-  const bool aligned = !(((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15);
+  const bool aligned = !(((uintptr_t)x | (uintptr_t)w | (uintptr_t)b | (uintptr_t)y) & 15);
   if ((H & 3) == 0 && H <= 8192 && aligned) {
     if (H <= 2048) {
       HB_DISPATCH_2(w_dt, y_dt, "hb_layernorm",
-                    (hb_launch(layernorm_vec_kernel<TA, TB, 2>, M, 256, 0, s, x, (const TA*)w, (TB*)y, rows, H, eps)));
+                    (hb_launch(layernorm_vec_kernel<TA, TB, 2>, M, 256, 0, s, x, (const TA*)w, (const TA*)b, (TB*)y, rows, H, eps)));
     } else {
       HB_DISPATCH_2(w_dt, y_dt, "hb_layernorm",
-                    (hb_launch(layernorm_vec_kernel<TA, TB, 8>, M, 256, 0, s, x, (const TA*)w, (TB*)y, rows, H, eps)));
+                    (hb_launch(layernorm_vec_kernel<TA, TB, 8>, M, 256, 0, s, x, (const TA*)w, (const TA*)b, (TB*)y, rows, H, eps)));
     }
   } else {
     HB_DISPATCH_2(w_dt, y_dt, "hb_layernorm",
-                  (hb_launch(layernorm_kernel<TA, TB>, M, 256, 0, s, x, (const TA*)w, (TB*)y, rows, H, eps)));
+                  (hb_launch(layernorm_kernel<TA, TB>, M, 256, 0, s, x, (const TA*)w, (const TA*)b, (TB*)y, rows, H, eps)));
   }
   HB_CHECK_LAUNCH("hb_layernorm");
   return 0;
@@ -427,27 +435,40 @@ HB_EXPORT int hb_gemm_simt(const void* A, int a_dt, long lda, const void* W, int
 // ---------------------------------------------------------------------------------------
 // SwiGLU over a gate/up matrix whose columns are interleaved in groups of `grp`
 // (grp gate columns, grp up columns, ...): act[m, i] = silu(g) * u, silu(g) = g / (1 + e^-g).
+// kind 1: the tanh form of GELU instead of silu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float hb_gate_act(float g, int kind) {
+  if (kind == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + expf(-g));
+}
+
 template <typename TI, typename TO>
-__global__ void swiglu_kernel(const TI* __restrict__ gu, long ld_gu, TO* __restrict__ act, long ld_act, int I, int grp) {
+__global__ void swiglu_kernel(const TI* __restrict__ gu, long ld_gu, TO* __restrict__ act, long ld_act, int I, int grp,
+                              int kind) {
   const TI* row = gu + (size_t)blockIdx.y * ld_gu;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= I) return;
   const int b = i / grp, j = i - b * grp;
   const float g = hb_to_float(row[(size_t)b * 2 * grp + j]), u = hb_to_float(row[(size_t)b * 2 * grp + grp + j]);
-  act[(size_t)blockIdx.y * ld_act + i] = hb_from_float<TO>(g / (1.f + expf(-g)) * u);
+  act[(size_t)blockIdx.y * ld_act + i] = hb_from_float<TO>(hb_gate_act(g, kind) * u);
+}
+
+// kind: 0 silu, 1 gelu (tanh form)
+HB_EXPORT int hb_gated_act(const void* gu, int gu_dt, long ld_gu, void* act, int act_dt, long ld_act, int M, int I, int grp,
+                           int kind, cudaStream_t s) {
+  if (M <= 0) return 0;
+  if (grp <= 0 || I % grp) HB_FAIL("hb_gated_act: width %d is not a multiple of the interleave group %d", I, grp);
+  if (M > 65535) HB_FAIL("hb_gated_act: M = %d is beyond the grid limit", M);
+  dim3 grid((I + 255) / 256, M);
+  HB_DISPATCH_2(gu_dt, act_dt, "hb_swiglu",
+                (swiglu_kernel<TA, TB><<<grid, 256, 0, s>>>((const TA*)gu, ld_gu, (TB*)act, ld_act, I, grp, kind)));
+  HB_CHECK_LAUNCH("hb_gated_act");
+  return 0;
 }
 
 HB_EXPORT int hb_swiglu(const void* gu, int gu_dt, long ld_gu, void* act, int act_dt, long ld_act, int M, int I, int grp,
                         cudaStream_t s) {
-  if (M <= 0) return 0;
-  if (grp <= 0 || I % grp) HB_FAIL("hb_swiglu: width %d is not a multiple of the interleave group %d", I, grp);
-  if (M > 65535) HB_FAIL("hb_swiglu: M = %d is beyond the grid limit", M);
-  dim3 grid((I + 255) / 256, M);
-  HB_DISPATCH_2(gu_dt, act_dt, "hb_swiglu",
-                (swiglu_kernel<TA, TB><<<grid, 256, 0, s>>>((const TA*)gu, ld_gu, (TB*)act, ld_act, I, grp)));
-  HB_CHECK_LAUNCH("hb_swiglu");
-  return 0;
+  return hb_gated_act(gu, gu_dt, ld_gu, act, act_dt, ld_act, M, I, grp, 0, s);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -570,6 +591,79 @@ HB_EXPORT int hb_rope_kv(const void* qkv, int qkv_dt, long ld, const int* pos, c
                 (rope_kv_kernel<TA, TB, TB><<<T, 256, 0, s>>>((const TA*)qkv, ld, pos, slot_map, (const float2*)table,
                                                               (TB*)q_out, (TB*)kc, (TB*)vc, Hq, Hkv, D, rot, page_size)));
   HB_CHECK_LAUNCH("hb_rope_kv");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Rotation, unit norm and cache write of a 32-bit projection result whose row holds q (H heads of D) at column q_off,
+// k (G heads of D) at k_off and v (G heads of E) at v_off. The first `rot` dimensions of every q and k head are rotated
+// by the row's position (pairs (i, i + rot/2) with pairing 0, (2i, 2i + 1) with pairing 1; the rest passes); then, if
+// asked, the head is divided by its root mean square over D (eps inside the root). q goes to q_out [T][H * D], k and v
+// to the token's page slot (planes [page][G][page_size][D] and [...][E]). All of it is 32-bit and rounded once.
+// No slot map (a layer that reads another layer's cache): q alone. A warp works on a head at a time.
+// ---------------------------------------------------------------------------------------
+template <typename TQ>
+__global__ void __launch_bounds__(256) rope_norm_store_kernel(const float* __restrict__ proj, long ld, int q_off, int k_off,
+                                                              int v_off, const int* __restrict__ pos,
+                                                              const int* __restrict__ slot_map,
+                                                              const float2* __restrict__ table, int rot, int pairing,
+                                                              int unit_norm, float eps, TQ* __restrict__ q_out,
+                                                              TQ* __restrict__ kc, TQ* __restrict__ vc, int H, int G, int D,
+                                                              int E, int page_size) {
+  extern __shared__ float rn_sh[];      // [8 warps][D]
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, half = rot >> 1;
+  const float* row = proj + (size_t)t * ld;
+  const float2* cs = table + (size_t)pos[t] * half;
+  const int slot = slot_map ? slot_map[t] : -1;
+  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  float* buf = rn_sh + warp * D;
+  const int n_heads = H + (slot >= 0 ? G : 0);
+  for (int hh = warp; hh < n_heads; hh += 8) {
+    const float* src = hh < H ? row + q_off + (size_t)hh * D : row + k_off + (size_t)(hh - H) * D;
+    for (int d = lane; d < D; d += 32) buf[d] = src[d];
+    __syncwarp();
+    float ss = 0.f;
+    for (int i = lane; i < half; i += 32) {
+      const int a = pairing ? 2 * i : i, b = pairing ? 2 * i + 1 : i + half;
+      const float u = buf[a], v = buf[b];
+      const float2 c = cs[i];
+      const float ru = __fsub_rn(__fmul_rn(u, c.x), __fmul_rn(v, c.y)), rv = __fadd_rn(__fmul_rn(v, c.x), __fmul_rn(u, c.y));
+      buf[a] = ru;
+      buf[b] = rv;
+    }
+    __syncwarp();
+    float f = 1.f;
+    if (unit_norm) {
+      for (int d = lane; d < D; d += 32) ss = fmaf(buf[d], buf[d], ss);
+      f = rsqrtf(hb_warp_sum(ss) / (float)D + eps);
+    }
+    TQ* dst = hh < H ? q_out + ((size_t)t * H + hh) * D : kc + ((page * G + (hh - H)) * page_size + off) * D;
+    for (int d = lane; d < D; d += 32) dst[d] = hb_from_float<TQ>(buf[d] * f);
+    __syncwarp();
+  }
+  if (slot < 0) return;
+  for (int i = threadIdx.x; i < G * E; i += 256) {
+    const int h = i / E, e = i - h * E;
+    vc[((page * G + h) * page_size + off) * E + e] = hb_from_float<TQ>(row[v_off + i]);
+  }
+}
+
+HB_EXPORT int hb_rope_norm_store(const float* proj, long ld, int q_off, int k_off, int v_off, const int* pos,
+                                 const int* slot_map, const void* table, int rot, int pairing, int unit_norm, float eps,
+                                 void* q_out, void* kc, void* vc, int q_dt, int T, int H, int G, int D, int E, int page_size,
+                                 cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (rot < 0 || rot > D || (rot & 1)) HB_FAIL("hb_rope_norm_store: %d rotated dimensions of a head of %d", rot, D);
+  if (slot_map && (!kc || !vc || G <= 0 || E <= 0 || page_size <= 0)) HB_FAIL("hb_rope_norm_store: a slot map without caches or sizes");
+  const size_t smem = (size_t)8 * D * sizeof(float);
+  if (smem > 48 * 1024) HB_FAIL("hb_rope_norm_store: heads of %d are too wide", D);
+  HB_DISPATCH_1(q_dt, "hb_rope_norm_store",
+                (hb_launch(rope_norm_store_kernel<TA>, T, 256, smem, s, proj, ld, q_off, k_off, v_off, pos, slot_map,
+                           (const float2*)table, rot, pairing, unit_norm, eps, (TA*)q_out, (TA*)kc, (TA*)vc, H, G, D, E,
+                           page_size)));
+  HB_CHECK_LAUNCH("hb_rope_norm_store");
   return 0;
 }
 

@@ -52,8 +52,9 @@ def main(argv=None) -> int:
     if 64 % a.page_size:
         raise SystemExit("trace_run: --page-size must divide 64")
     num_pages = -(-a.max_tokens // 64) * (64 // a.page_size)
+    # no request holds more than the pool: tables of positions and block tables are made for that length at most
     runner = ModelRunner.from_folder(a.model, dtype=a.dtype, page_size=a.page_size, num_pages=num_pages,
-                                     max_num_seqs=a.max_requests)
+                                     max_num_seqs=a.max_requests, max_model_len=num_pages * a.page_size)
     for line in sys.stdin:
         line = line.strip()
         if not line:

@@ -276,6 +276,11 @@ def linear_swiglu(a, w, act_out, group) -> bool:
     return True
 
 
+def linear_gated(a, w, act_out, group, act) -> bool:
+    """The gate/up product with the activation in its epilogue: "silu" only so far."""
+    return act == "silu" and linear_swiglu(a, w, act_out, group)
+
+
 # ------------------------------------------------------------------------------------------
 # a few token rows (csrc/gemm_rows.cu): whole-K output stripes, norm in the prologue, the layer's
 # own arithmetic in the epilogue; a decoder layer of a small decode step is five kernels

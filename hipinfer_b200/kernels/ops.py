@@ -33,12 +33,21 @@ _SIGS = {
         "hb_convert": [_p, _i, _p, _i, _l, _p],
         "hb_feed_tokens": [_p, _p, _p, _i, _p],
         "hb_embed_pos": [_p, _p, _i, _p, _p, _p, _i, _i, _f, _p],
-        "hb_layernorm": [_p, _p, _i, _p, _i, _p, _i, _i, _f, _p],
+        "hb_layernorm": [_p, _p, _p, _i, _p, _i, _p, _i, _i, _f, _p],
+        "hb_gated_act": [_p, _i, _l, _p, _i, _l, _i, _i, _i, _i, _p],
+        "hb_rope_norm_store": [_p, _l, _i, _i, _i, _p, _p, _p, _i, _i, _i, _f, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
         "hb_polynorm": [_p, _l, _p, _i, _l, _i, _i, _f, _f, _f, _f, _f, _p],
         "hb_scale_add": [_p, _p, _l, _p, _i, _i, _i, _p],
         "hb_bias_act": [_p, _l, _p, _i, _p, _i, _l, _i, _i, _i, _p],
         "hb_qkv_bias_store": [_p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
         "hb_gemm_simt_scaled": [_p, _i, _l, _p, _i, _l, _p, _l, _i, _i, _i, _p, _p],
+    },
+    "seqmix": {
+        "hb_attn_masked": [_p, _i, _l, _p, _l, _p, _l, _i, _p, _i, _p, _p, _p, _p, _l, _i, _i, _p, _i, _l, _i, _i, _i, _i, _i,
+                           _i, _i, _i, _i, _i, _f, _p, _i, _p, _l, _p, _i, _p],
+        "hb_latent_prepare": [_p, _l, _i, _i, _i, _p, _p, _i, _p, _p, _p, _i, _f, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+        "hb_heads_linear": [_p, _l, _l, _p, _i, _p, _i, _l, _l, _i, _i, _i, _i, _p, _l, _i, _i, _i, _p, _p, _p],
+        "hb_gla": [_p, _l, _i, _i, _i, _i, _p, _l, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _f, _p],
     },
     "mixers": {
         "hb_delta_rule": [_p, _l, _i, _i, _i, _i, _i, _p, _l, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _f,
@@ -146,9 +155,11 @@ def embedding_scaled(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tenso
 
 
 def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[i] = weight * (x[r] - mean) / sqrt(var + eps), r = rows[i] or i; x float32 [*, H]; no bias."""
-    _need_cuda(x, weight, out, rows)
+              rows: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = weight * (x[r] - mean) / sqrt(var + eps) (+ bias), r = rows[i] or i; x float32 [*, H]."""
+    _need_cuda(x, weight, out, rows, bias)
+    if bias is not None:
+        assert bias.numel() == weight.numel() and bias.dtype == weight.dtype and bias.is_contiguous()
     M, H = out.shape
     assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and x.shape[1] == H
     assert weight.numel() == H and weight.is_contiguous()
@@ -156,7 +167,7 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tens
         assert rows.dtype == torch.int32 and rows.numel() == M
     else:
         assert x.shape[0] == M
-    _call("core", "hb_layernorm", x.data_ptr(), weight.data_ptr(), _dt(weight), out.data_ptr(), _dt(out), _ptr(rows),
+    _call("core", "hb_layernorm", x.data_ptr(), weight.data_ptr(), _ptr(bias), _dt(weight), out.data_ptr(), _dt(out), _ptr(rows),
           M, H, float(eps), _stream())
     return out
 
@@ -680,3 +691,178 @@ def attention(q, k_cache, v_cache, batch, group: int, out, n_heads, n_kv_heads, 
         return out
     return attention_rows(q, k_cache, v_cache, batch.block_tables[group], batch.row_request, batch.positions, out,
                           n_heads, n_kv_heads, head_dim, page_size, window, scale, batch.max_pos)
+
+
+# ------------------------------------------------------------------------------------------
+# Operations of gated feed-forwards, of attention with a mask, a sink and a gate chosen by parameters, of latent
+# attention and of gated linear attention (csrc/core.cu, attention_masked.cu, latent.cu, gla.cu)
+# ------------------------------------------------------------------------------------------
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, group: int, act: str = "silu") -> torch.Tensor:
+    """out[m, i] = act(g) * u for a gate/up matrix [M, 2I] interleaved in groups of `group` columns; act "silu" or
+    "gelu_tanh" (0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))))."""
+    _need_cuda(gate_up, out)
+    _rows_contiguous(gate_up, "gated_act in")
+    _rows_contiguous(out, "gated_act out")
+    M, I = out.shape
+    assert gate_up.shape == (M, 2 * I)
+    _call("core", "hb_gated_act", gate_up.data_ptr(), _dt(gate_up), gate_up.stride(0), out.data_ptr(), _dt(out),
+          out.stride(0), M, I, group, GATE_ACTS[act], _stream())
+    return out
+
+
+def linear_gated(a: torch.Tensor, w_gate_up: "Weight", act_out: torch.Tensor, group: int, act: str) -> bool:
+    """act_out = act(gate) * up of a @ w_gate_up.T as one kernel (the activation in the product's epilogue) where one
+    takes these sizes; False: nothing was done (the caller runs the product, then gated_act)."""
+    from . import fast
+
+    return a.is_cuda and fast.linear_gated(a, w_gate_up, act_out, group, act)
+
+
+_rope_tables = {}
+
+
+def shared_rope_table(dims: int, base: float, n_pos: int, device) -> torch.Tensor:
+    """(cos, sin) float32 [n_pos, dims / 2, 2] of the angles p * base^(-2i / dims): one table per (dims, base, n_pos,
+    device), shared by every part that asks (the frequencies are computed in float64 and rounded to float32)."""
+    key = (int(dims), float(base), int(n_pos), str(device))
+    t = _rope_tables.get(key)
+    if t is None:
+        i = torch.arange(0, dims, 2, dtype=torch.float64)
+        inv = torch.pow(torch.tensor(float(base), dtype=torch.float64), -i / dims).to(torch.float32)
+        t = _rope_tables[key] = rope_table(inv.to(device), n_pos)
+    return t
+
+
+PAIRINGS = {"half": 0, "interleaved": 1}
+
+
+def rope_norm_store(proj: torch.Tensor, offsets, positions: torch.Tensor, slot_map: Optional[torch.Tensor],
+                    table: torch.Tensor, rot: int, pairing: str, unit_norm: bool, eps: float, q_out: torch.Tensor,
+                    k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], n_heads: int, n_kv_heads: int,
+                    dim: int, vdim: int, page_size: int) -> torch.Tensor:
+    """From a float32 projection result whose rows hold q, k, v at the column `offsets` (q, k, v): q and k rotated on
+    their first `rot` dimensions (pairing "half": (i, i + rot/2); "interleaved": (2i, 2i + 1)) and, with unit_norm,
+    divided by their root mean square over `dim`; q to q_out [T, n_heads * dim], k and v (vdim wide, raw) to their page
+    slots. slot_map None: q alone."""
+    _need_cuda(proj, positions, slot_map, table, q_out, k_cache, v_cache)
+    _rows_contiguous(proj, "rope_norm_store in")
+    T = proj.shape[0]
+    assert proj.dtype == torch.float32 and q_out.is_contiguous() and q_out.shape == (T, n_heads * dim)
+    assert table.dtype == torch.float32 and table.is_contiguous() and table.shape[1] * 2 == rot
+    if slot_map is not None:
+        assert k_cache.dtype == v_cache.dtype == q_out.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert k_cache.shape[-1] == dim and v_cache.shape[-1] == vdim
+    q_off, k_off, v_off = (int(o) for o in offsets)
+    _call("core", "hb_rope_norm_store", proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, positions.data_ptr(),
+          _ptr(slot_map), table.data_ptr(), int(rot), PAIRINGS[pairing], 1 if unit_norm else 0, float(eps), q_out.data_ptr(),
+          _ptr(k_cache) if slot_map is not None else None, _ptr(v_cache) if slot_map is not None else None, _dt(q_out), T,
+          n_heads, n_kv_heads, dim, vdim, page_size, _stream())
+    return q_out
+
+
+MASKS = {"causal": 0, "window": 1, "chunk": 2}
+MASKED_FLASH_MIN_ROWS = 16
+
+
+def attention_masked(q, k_cache, v_cache, batch, group: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
+                     page_size: int, scale: float, mask: str = "causal", window: int = 0, keep_first: int = 0, chunk: int = 0,
+                     sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_offset: int = 0,
+                     gate_per_head: bool = False, force_rows: bool = False) -> torch.Tensor:
+    """Attention of the step's rows over their requests' pages (csrc/attention_masked.cu): keys `dim` and values `vdim`
+    wide, each plane [page, kv head, page_size, width] with a width of its own (v_cache may be the key plane itself:
+    the values are then its first `vdim` columns). mask "causal", "window" (the last `window` keys and the first
+    `keep_first`) or "chunk" (the keys of the row's own chunk of `chunk` positions). sink: float32 [n_heads], joins the
+    softmax's denominator as exp(sink). gate: float32 [T, *], sigmoid(gate[:, gate_offset + ...]) multiplies the result,
+    one number per element or, with gate_per_head, one per head. out may be float32 beside bfloat16 q."""
+    _need_cuda(q, k_cache, v_cache, out, gate, sink)
+    T = q.shape[0]
+    bt = batch.block_tables[group]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == k_cache.dtype == v_cache.dtype
+    assert q.shape[1] == n_heads * dim and out.shape == (T, n_heads * vdim)
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape[-1] >= dim and v_cache.shape[-1] >= vdim
+    assert k_cache.shape[1] == n_kv_heads
+    if sink is not None:
+        assert sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous()
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == T
+    lib = library.load("seqmix")
+    lib.hb_attn_masked_workspace.restype = C.c_long
+    lib.hb_attn_masked_workspace.argtypes = [_i] * 10
+    lib.hb_attn_masked_counters.argtypes = [_i] * 5
+    max_pos = int(getattr(batch, "max_pos", 0)) or int(bt.shape[1]) * page_size - 1
+    m = MASKS[mask]
+    n_ws = lib.hb_attn_masked_workspace(T, n_heads, n_kv_heads, dim, vdim, m, int(window), int(keep_first), int(chunk), max_pos)
+    ws = arrived = None
+    if n_ws:
+        from . import fast
+
+        ws = torch.empty(n_ws, dtype=torch.float32, device=q.device)
+        arrived = fast._decode_counters(q.device, lib.hb_attn_masked_counters(T, n_heads, n_kv_heads, dim, vdim))
+    _call("seqmix", "hb_attn_masked", q.data_ptr(), _dt(q), q.stride(0), k_cache.data_ptr(), k_cache.shape[-1],
+          v_cache.data_ptr(), v_cache.shape[-1], _dt(k_cache), bt.data_ptr(), bt.stride(0), batch.row_request.data_ptr(),
+          batch.positions.data_ptr(), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, int(gate_offset),
+          (2 if gate_per_head else 1) if gate is not None else 0, out.data_ptr(), _dt(out), out.stride(0), T, n_heads,
+          n_kv_heads, dim, vdim, page_size, m, int(window), int(keep_first), int(chunk), float(scale), None, 0, _ptr(ws),
+          n_ws, _ptr(arrived), max_pos, _stream())
+    return out
+
+
+def latent_prepare(proj: torch.Tensor, offsets, wq: torch.Tensor, wc: torch.Tensor, positions, slot_map, table, rot: int,
+                   eps: float, cq_out: torch.Tensor, cache: Optional[torch.Tensor], q_rank: int, kv_rank: int, rot_dim: int,
+                   page_size: int) -> torch.Tensor:
+    """From a float32 projection result with the raw query latent, the raw key/value latent and the raw rotated key part
+    at the column `offsets`: the query latent / rms * wq to cq_out [T, q_rank]; the key/value latent / rms * wc and the
+    rotated key part (pairs (2i, 2i + 1)) to the token's row of `cache` [page, 1, page_size, kv_rank + rot_dim]."""
+    _need_cuda(proj, wq, wc, positions, slot_map, table, cq_out, cache)
+    _rows_contiguous(proj, "latent_prepare in")
+    T = proj.shape[0]
+    assert proj.dtype == torch.float32 and cq_out.is_contiguous() and cq_out.shape == (T, q_rank)
+    assert wq.dtype == wc.dtype and wq.numel() == q_rank and wc.numel() == kv_rank
+    if slot_map is not None:
+        assert cache.is_contiguous() and cache.dtype == cq_out.dtype and cache.shape[1] == 1 and cache.shape[-1] == kv_rank + rot_dim
+    a, b, c = (int(o) for o in offsets)
+    _call("seqmix", "hb_latent_prepare", proj.data_ptr(), proj.stride(0), a, b, c, wq.data_ptr(), wc.data_ptr(), _dt(wq),
+          positions.data_ptr(), _ptr(slot_map), table.data_ptr(), int(rot), float(eps), cq_out.data_ptr(),
+          _ptr(cache) if slot_map is not None else None, _dt(cq_out), T, q_rank, kv_rank, rot_dim, page_size, _stream())
+    return cq_out
+
+
+def heads_linear(a: torch.Tensor, a_head: int, wt: torch.Tensor, out: torch.Tensor, o_head: int, gate=None,
+                 gate_offset: int = 0, tail: int = 0, rot: int = 0, positions=None, table=None) -> torch.Tensor:
+    """out[t, h * o_head + n] = sum_k a[t, h * a_head + k] wt[h, k, n] for every head h (a float32, 32-bit sums),
+    optionally times sigmoid(gate[t, gate_offset + h * N + n]); with `tail`, the tail columns behind a head's K inputs
+    are rotated on their first `rot` (pairs (2i, 2i + 1)) by the row's position and copied behind its N outputs."""
+    _need_cuda(a, wt, out, gate, positions, table)
+    _rows_contiguous(a, "heads_linear a")
+    _rows_contiguous(out, "heads_linear out")
+    H, K, N = wt.shape
+    T = a.shape[0]
+    assert a.dtype == torch.float32 and wt.is_contiguous() and out.shape[0] == T
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1
+    _call("seqmix", "hb_heads_linear", a.data_ptr(), a.stride(0), int(a_head), wt.data_ptr(), _dt(wt), out.data_ptr(),
+          _dt(out), out.stride(0), int(o_head), T, H, K, N, _ptr(gate), gate.stride(0) if gate is not None else 0,
+          int(gate_offset), int(tail), int(rot), _ptr(positions), _ptr(table), _stream())
+    return out
+
+
+def gla(proj: torch.Tensor, offsets, z: torch.Tensor, a_bias, norm_weight, state: torch.Tensor, batch, out: torch.Tensor,
+        heads: int, dim: int, vdim: int, tau: float, eps: float) -> torch.Tensor:
+    """Gated linear attention over the step's rows, request by request, from and into each request's state slot
+    (csrc/gla.cu). proj float32 [T, *] holds q, k, v and the gate's pre-activation at the column `offsets` (q, k, v, g);
+    z float32 [T, heads * dim] the decay's pre-activation without its bias; state float32 [slots, heads, dim, vdim]."""
+    _need_cuda(proj, z, a_bias, norm_weight, state, out)
+    _rows_contiguous(proj, "gla proj")
+    _rows_contiguous(z, "gla z")
+    assert proj.dtype == z.dtype == state.dtype == torch.float32 and state.is_contiguous() and out.is_contiguous()
+    assert state.shape[1:] == (heads, dim, vdim) and out.shape == (proj.shape[0], heads * vdim)
+    assert a_bias.dtype == norm_weight.dtype and a_bias.numel() == heads * dim and norm_weight.numel() == vdim
+    q, k, v, g = (int(o) for o in offsets)
+    _call("seqmix", "hb_gla", proj.data_ptr(), proj.stride(0), q, k, v, g, z.data_ptr(), z.stride(0), a_bias.data_ptr(),
+          norm_weight.data_ptr(), _dt(a_bias), state.data_ptr(), batch.req_q_start.data_ptr(), batch.req_q_len.data_ptr(),
+          batch.req_state_slot.data_ptr(), out.data_ptr(), _dt(out), batch.n_requests, heads, dim, vdim, float(tau),
+          float(eps), _stream())
+    return out

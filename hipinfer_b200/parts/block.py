@@ -177,5 +177,46 @@ class ScaledPreNormBlock(Part):
         return None
 
 
+class ParallelBlock(Part):
+    """One norm, two readers: h = norm(x); x += mixer(h) + feed_forward(h). Both sublayers read the same normalised rows
+    and add into the 32-bit residual stream; the feed-forward is optional (a layer that gives none has the mixer only).
+    params: layer (the LayerSpec) with the parts `norm`, `mixer` and, optionally, `feed_forward`."""
+
+    SLOTS = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        layer = params["layer"]
+        has_ff = "feed_forward" in layer.parts
+        self.parts = build_slots(self, layer, {n: r for n, r in self.SLOTS.items() if has_ff or n != "feed_forward"}, ctx, prefix)
+        if not has_ff:
+            self.feed_forward = None
+
+    def param_specs(self):
+        return [s for p in self.parts for s in p.param_specs()]
+
+    def load(self, tensors):
+        for p in self.parts:
+            p.load(tensors)
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self.parts)
+
+    def forward(self, x, batch, cache, state):
+        h = self.norm.forward(x)
+        planes.record(batch, "mixer_norm", h)
+        left = self.mixer.forward(h, x, batch, cache, state)
+        if isinstance(left, ops.Pending):
+            left.finish()
+        planes.record(batch, "after_mixer", x)
+        if self.feed_forward is not None:
+            left = self.feed_forward.forward(h, x, batch)
+            if isinstance(left, ops.Pending):
+                left.finish()
+        planes.record(batch, "after_feed_forward", x)
+        return None
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)
 register_part("block", "pre_norm_scaled", ScaledPreNormBlock)

@@ -7,7 +7,7 @@ import torch
 
 from ..kernels import ops
 from ..weights import ParamSpec
-from .registry import Part, register_part, to_compute
+from .registry import Part, build_part, register_part, to_compute
 
 
 class TokenEmbedding(Part):
@@ -60,6 +60,30 @@ class ScaledPositionEmbedding(Part):
         return ops.embedding_scaled(self.table, tokens, x, self.scale, self.position_table, positions)
 
 
+class NormedTokenEmbedding(Part):
+    """x = norm(table[token]): a token embedding whose rows go through a norm of the model's kind before they enter the
+    32-bit residual stream (the norm's result stays 32-bit). params: name, vocab_size, hidden_size, norm (the PartSpec
+    of a norm over hidden_size)."""
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        self.name, self.vocab, self.hidden = params["name"], int(params["vocab_size"]), int(params["hidden_size"])
+        self.norm = build_part("norm", params["norm"], ctx, prefix)
+        self.table = None
+
+    def param_specs(self):
+        return [ParamSpec(self.name, (self.vocab, self.hidden))] + self.norm.param_specs()
+
+    def load(self, tensors):
+        self.table = to_compute(tensors[self.name], self.ctx)
+        self.norm.load(tensors)
+
+    def forward(self, tokens):
+        raw = torch.empty(tokens.numel(), self.hidden, dtype=torch.float32, device=tokens.device)
+        ops.embedding(self.table, tokens, raw)
+        return self.norm.forward(raw, out=torch.empty_like(raw))
+
+
 class LMHead(Part):
     """params: name (its own tensor) or tied_to (the embedding's tensor name), vocab_size, hidden_size."""
 
@@ -88,4 +112,5 @@ class LMHead(Part):
 
 register_part("embedding", "token", TokenEmbedding)
 register_part("embedding", "token_position", ScaledPositionEmbedding)
+register_part("embedding", "token_normed", NormedTokenEmbedding)
 register_part("head", "linear", LMHead)

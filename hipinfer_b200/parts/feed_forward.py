@@ -62,6 +62,51 @@ class SwiGLU(Part):
         return ops.linear_deferred(act, self.wdown, x, accumulate=True)   # the next norm may add it
 
 
+class GatedFF(Part):
+    """A gated dense feed-forward with a choice of activation: out = Wdown (act(Wgate h) * (Wup h)), act "silu" or
+    "gelu_tanh" (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))). Gate and up are one product; its 32-bit result feeds
+    the activation, which is rounded once. Any intermediate size: rows are interleaved in groups of 16 where the size
+    is a multiple of 16 (the layout the fused kernels of SwiGLU read), else the gate rows come first.
+
+    params: hidden_size, intermediate_size, activation, gate_name, up_name, down_name."""
+
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.act = params.get("activation", "silu")
+        if self.act not in ops.GATE_ACTS:
+            raise ValueError(f"gated feed-forward: activation {self.act!r} is not known (known: {sorted(ops.GATE_ACTS)})")
+        self.group = GROUP if self.inter % GROUP == 0 else self.inter
+        self.names = {k: prefix + params.get(k + "_name", f"mlp.{k}") for k in ("gate", "up", "down")}
+        self.wgu = self.wdown = None
+
+    def param_specs(self):
+        return [ParamSpec(self.names["gate"], (self.inter, self.hidden)), ParamSpec(self.names["up"], (self.inter, self.hidden)),
+                ParamSpec(self.names["down"], (self.hidden, self.inter))]
+
+    def load(self, tensors):
+        g, u = to_compute(tensors[self.names["gate"]], self.ctx), to_compute(tensors[self.names["up"]], self.ctx)
+        dt = g.dtype if g.dtype == u.dtype else torch.float32
+        I, H, G = self.inter, self.hidden, self.group
+        gu = torch.stack([g.to(dt).reshape(I // G, G, H), u.to(dt).reshape(I // G, G, H)], 1)
+        self.wgu = ops.Weight(gu.reshape(2 * I, H).contiguous())
+        self.wdown = ops.Weight(to_compute(tensors[self.names["down"]], self.ctx))
+
+    def weight_bytes(self):
+        return self.wgu.nbytes + self.wdown.nbytes
+
+    def forward(self, xn, x, batch):
+        T = xn.shape[0]
+        act = torch.empty(T, self.inter, dtype=self.ctx.dtype, device=xn.device)
+        if not ops.linear_gated(xn, self.wgu, act, self.group, self.act):
+            gu = torch.empty(T, 2 * self.inter, dtype=torch.float32, device=xn.device)
+            ops.linear(xn, self.wgu, gu)
+            ops.gated_act(gu, act, self.group, self.act)
+        planes.record(batch, "activation", act)
+        ops.linear(act, self.wdown, x, accumulate=True)
+        return None
+
+
 class PolyNormFF(Part):
     """A dense feed-forward without a gate: out = act(xn Wup^T) Wdown^T with the PolyNorm activation
     act(z) = c1 N(z) + c2 N(z^2) + c3 N(z^3) + c0, powers element by element, N(t) = t / sqrt(mean(t^2) + eps) over
@@ -107,3 +152,4 @@ class PolyNormFF(Part):
 
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "polynorm", PolyNormFF)
+register_part("feed_forward", "gated", GatedFF)

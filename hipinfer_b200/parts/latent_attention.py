@@ -1,0 +1,101 @@
+"""Latent attention: queries, keys and values go through low-rank latents, and the cache keeps one latent and one rotated
+key part per token instead of keys and values of every head.
+
+    cq = Wdq h / rms(Wdq h) * wq                         the query latent (q_rank wide; eps inside the root)
+    q_h = Wuq_h cq = [plain (dim) | rotated (rot_dim)]    per head
+    [c_raw | kr_raw] = Wdkv h;  c = c_raw / rms(c_raw) * wc (kv_rank wide);  kr = rotated(kr_raw) (rot_dim, one for all heads)
+    k_h = Wuk_h c,  v_h = Wuv_h c                         (dim and vdim wide)
+    score = (q_plain . k_h + q_rot . kr) * scale, causal softmax, heads concatenated, times sigmoid(Wg h), then Wo
+
+The rotation pairs dimensions (2i, 2i + 1) of the rotated parts, i < rot_dims / 2, by the angle p * base^(-2i / rot_dims).
+Only c and kr are cached: one plane of kv_rank + rot_dim columns and one "head" per token. Attention runs in the
+latent's space: the query's plain part is taken there once per row (Wuk_h^T q_plain, kv_rank wide), a row's pass over
+the cache reads [c | kr] rows as keys and their first kv_rank columns as values, and Wuv_h is applied to the summed
+latent (csrc/latent.cu). Root mean squares, angles, scores, softmax and the gate are 32-bit; the query that enters
+attention and the gated heads are rounded once each, the summed latent stays 32-bit.
+
+params: hidden_size, heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, eps, rot_dims (default rot_dim), rot_base, and the
+tensor names dq, dq_norm, uq, dkv, dkv_norm, uk, uv, g, o (`<key>_name`).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights import ParamSpec
+from . import planes
+from .registry import CacheNeed, Mixer, register_part, to_compute
+
+_DEFAULT_NAMES = dict(dq="mix.dq", dq_norm="mix.dq.norm", uq="mix.uq", dkv="mix.dkv", dkv_norm="mix.dkv.norm", uk="mix.uk",
+                      uv="mix.uv", g="mix.g", o="mix.o")
+
+
+class LatentAttentionMixer(Mixer):
+    def __init__(self, params, ctx, prefix=""):
+        super().__init__(params, ctx, prefix)
+        p = params
+        self.hidden, self.heads = int(p["hidden_size"]), int(p["heads"])
+        self.dim, self.rot_dim, self.vdim = int(p["dim"]), int(p["rot_dim"]), int(p["vdim"])
+        self.q_rank, self.kv_rank = int(p["q_rank"]), int(p["kv_rank"])
+        self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        self.rot_dims, self.rot_base = int(p.get("rot_dims", self.rot_dim)), float(p.get("rot_base", 10000.0))
+        if self.rot_dims % 2 or self.rot_dims > self.rot_dim:
+            raise ValueError(f"latent attention: {self.rot_dims} rotated dimensions of a rotated part of {self.rot_dim}")
+        self.names = {k: prefix + p.get(k + "_name", d) for k, d in _DEFAULT_NAMES.items()}
+        self.w_in = self.w_uq = self.wo = self.wuk_t = self.wuv_t = self.table = None
+        if not ctx.is_meta:
+            self.table = ops.shared_rope_table(self.rot_dims, self.rot_base, ctx.max_model_len, ctx.device)
+
+    def param_specs(self):
+        n, W, H = self.names, self.hidden, self.heads
+        return [ParamSpec(n["dq"], (self.q_rank, W)), ParamSpec(n["dq_norm"], (self.q_rank,), init="ones"),
+                ParamSpec(n["uq"], (H * (self.dim + self.rot_dim), self.q_rank)),
+                ParamSpec(n["dkv"], (self.kv_rank + self.rot_dim, W)), ParamSpec(n["dkv_norm"], (self.kv_rank,), init="ones"),
+                ParamSpec(n["uk"], (H * self.dim, self.kv_rank)), ParamSpec(n["uv"], (H * self.vdim, self.kv_rank)),
+                ParamSpec(n["g"], (H * self.vdim, W)), ParamSpec(n["o"], (W, H * self.vdim))]
+
+    def load(self, tensors):
+        t = {k: to_compute(tensors[n], self.ctx) for k, n in self.names.items()}
+        mats = [t["dq"], t["dkv"], t["g"]]
+        dt = mats[0].dtype if all(m.dtype == mats[0].dtype for m in mats) else torch.float32
+        self.w_in = ops.Weight(torch.cat([m.to(dt) for m in mats], 0).contiguous())      # rows [dq | dkv | g]
+        self.w_uq, self.wo = ops.Weight(t["uq"]), ops.Weight(t["o"])
+        H = self.heads
+        self.wuk_t = t["uk"].reshape(H, self.dim, self.kv_rank).contiguous()                      # [h][d][r]
+        self.wuv_t = t["uv"].reshape(H, self.vdim, self.kv_rank).transpose(1, 2).contiguous()     # [h][r][e]
+        self.wq_norm, self.wc_norm = t["dq_norm"], t["dkv_norm"].to(t["dq_norm"].dtype)
+
+    def weight_bytes(self):
+        return (self.w_in.nbytes + self.w_uq.nbytes + self.wo.nbytes
+                + sum(w.numel() * w.element_size() for w in (self.wuk_t, self.wuv_t)))
+
+    def cache_need(self):
+        width = self.kv_rank + self.rot_dim
+        return CacheNeed("full", 1, width, 0, (("ckr", 1, width),))
+
+    def forward(self, xn, x, batch, cache, state):
+        T, H, dev = xn.shape[0], self.heads, xn.device
+        Rq, R, Dr, D, E = self.q_rank, self.kv_rank, self.rot_dim, self.dim, self.vdim
+        proj = torch.empty(T, Rq + R + Dr + H * E, dtype=torch.float32, device=dev)
+        ops.linear(xn, self.w_in, proj)
+        ckr = cache.planes["ckr"]
+        cq = torch.empty(T, Rq, dtype=self.ctx.dtype, device=dev)
+        ops.latent_prepare(proj, (0, Rq, Rq + R), self.wq_norm, self.wc_norm, batch.positions,
+                           batch.slot_maps[cache.group] if cache.write else None, self.table, self.rot_dims, self.eps, cq, ckr,
+                           Rq, R, Dr, self.ctx.page_size)
+        q = torch.empty(T, H * (D + Dr), dtype=torch.float32, device=dev)
+        ops.linear(cq, self.w_uq, q)
+        qa = torch.empty(T, H * (R + Dr), dtype=self.ctx.dtype, device=dev)        # per head [Wuk^T q_plain | rotated part]
+        ops.heads_linear(q, D + Dr, self.wuk_t, qa, R + Dr, tail=Dr, rot=self.rot_dims, positions=batch.positions,
+                         table=self.table)
+        lat = torch.empty(T, H * R, dtype=torch.float32, device=dev)               # per head the softmax-weighted sum of c
+        ops.attention_masked(qa, ckr, ckr, batch, cache.group, lat, H, 1, R + Dr, R, self.ctx.page_size, self.scale, "causal")
+        att = torch.empty(T, H * E, dtype=self.ctx.dtype, device=dev)
+        ops.heads_linear(lat, R, self.wuv_t, att, E, gate=proj, gate_offset=Rq + R + Dr)
+        planes.record(batch, "q", qa)
+        planes.record(batch, "attention", att)
+        ops.linear(att, self.wo, x, accumulate=True)
+        return None
+
+
+register_part("mixer", "latent_attention", LatentAttentionMixer)

@@ -54,29 +54,36 @@ class RMSNorm(Part):
 
 
 class LayerNorm(Part):
-    """Layer norm with a weight and no bias: y = w * (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps), computed in 32-bit
-    from the 32-bit residual stream and rounded once. params: name (tensor name relative to the prefix), size, eps."""
+    """Layer norm with a weight and, where `bias_name` is given, a bias: y = w * (x - mean(x)) / sqrt(mean((x - mean(x))^2)
+    + eps) + b, computed in 32-bit from the 32-bit residual stream and rounded once. params: name (tensor name relative
+    to the prefix), size, eps, bias_name (absent: no bias). `out` may be a 32-bit tensor (a norm inside the stream)."""
 
     def __init__(self, params, ctx, prefix=""):
         super().__init__(params, ctx, prefix)
         self.size, self.eps = int(params["size"]), float(params["eps"])
         self.name = prefix + params["name"]
-        self.weight = None
+        self.bias_name = prefix + params["bias_name"] if params.get("bias_name") else None
+        self.weight = self.bias = None
 
     def param_specs(self):
-        return [ParamSpec(self.name, (self.size,), init="ones")]
+        specs = [ParamSpec(self.name, (self.size,), init="ones")]
+        if self.bias_name:
+            specs.append(ParamSpec(self.bias_name, (self.size,), init="zeros"))
+        return specs
 
     def load(self, tensors):
         self.weight = to_compute(tensors[self.name], self.ctx)
+        if self.bias_name:
+            self.bias = to_compute(tensors[self.bias_name], self.ctx).to(self.weight.dtype)
 
     def weight_bytes(self):
-        return self.weight.numel() * self.weight.element_size()
+        return self.weight.numel() * self.weight.element_size() * (2 if self.bias is not None else 1)
 
     def forward(self, x, rows=None, out=None):
         M = x.shape[0] if rows is None else rows.numel()
         if out is None:
             out = torch.empty(M, self.size, dtype=self.ctx.dtype, device=x.device)
-        return ops.layernorm(x, self.weight, self.eps, out, rows)
+        return ops.layernorm(x, self.weight, self.eps, out, rows, self.bias)
 
 
 register_part("norm", "rmsnorm", RMSNorm)
