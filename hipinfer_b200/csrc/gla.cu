@@ -29,8 +29,11 @@ struct GlaArgs {
   float inv_tau, eps, q_scale;
 };
 
+// threads a block may have so that DPT state values (and what goes with them) stay in registers
+template <int DPT> struct GlaThreads { static constexpr int MAX = DPT <= 8 ? 1024 : DPT <= 32 ? 512 : 256; };
+
 template <int DPT, typename TW, typename TO>
-__global__ void gla_kernel(GlaArgs A) {
+__global__ void __launch_bounds__(GlaThreads<DPT>::MAX, 1) gla_kernel(GlaArgs A) {
   extern __shared__ float gsm[];
   hb_pdl_launch();
   hb_pdl_wait();
@@ -114,11 +117,19 @@ HB_EXPORT int hb_gla(const float* proj, long ld, int q_off, int k_off, int v_off
                      cudaStream_t s) {
   if (n_requests <= 0) return 0;
   if (E > 1024) HB_FAIL("hb_gla: values of %d are too wide", E);
-  // threads a value channel: enough that a thread holds at most DPT key channels, more while the block is small
-  int ks = 1;
-  while (((D + ks - 1) / ks > 32 || ((long)E * ks < 256 && ks < 8)) && ks < 32 && (long)E * ks * 2 <= 1024) ks *= 2;
+  // threads a value channel (a power of two up to 32): the fewest that give the block 256 threads, else the most that
+  // fit; a thread holds ceil(D / ks) key channels of its value channel, which bounds the block's threads
+  int ks = 0;
+  for (int c = 1; c <= 32; c *= 2) {
+    const int per_c = (D + c - 1) / c, threads_c = ((E * c + 31) / 32) * 32;
+    if (per_c > 64) continue;
+    const int limit = per_c <= 8 ? 1024 : per_c <= 32 ? 512 : 256;
+    if (threads_c > limit) break;
+    ks = c;
+    if (threads_c >= 256) break;
+  }
+  if (!ks) HB_FAIL("hb_gla: heads of %d x %d do not fit a block's registers", D, E);
   const int per = (D + ks - 1) / ks;
-  if (per > 64) HB_FAIL("hb_gla: heads of %d x %d do not fit a block's registers", D, E);
   GlaArgs A;
   A.proj = proj; A.ld = ld; A.q_off = q_off; A.k_off = k_off; A.v_off = v_off; A.g_off = g_off; A.z = z; A.ldz = ldz;
   A.a_bias = a_bias; A.norm_w = norm_w; A.state = state; A.q_start = q_start; A.q_len = q_len; A.slot = slot; A.out = out;

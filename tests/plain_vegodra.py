@@ -186,3 +186,19 @@ def forward(config, weights, tokens, layers_out=None):
             layers_out.append(x.clone())
     x = layer_norm(x, w["final.norm"], w["final.norm.b"], eps)
     return x @ w["head"].T
+
+
+class PlainVegodra:
+    """The whole model with a memory of the tokens it was given: forward(tokens) appends them to the sequence, computes
+    the whole sequence anew and returns the logits of the new tokens. reset() starts another sequence."""
+
+    def __init__(self, config, weights):
+        self.config, self.weights, self.tokens = config, weights, []
+
+    def reset(self):
+        self.tokens = []
+
+    def forward(self, tokens):
+        n = len(self.tokens)
+        self.tokens = self.tokens + [int(t) for t in tokens]
+        return forward(self.config, self.weights, self.tokens)[n:]
