@@ -596,8 +596,8 @@ HB_EXPORT int hb_rope_kv(const void* qkv, int qkv_dt, long ld, const int* pos, c
 
 // ---------------------------------------------------------------------------------------
 // Rotation, unit norm and cache write of a 32-bit projection result whose row holds q (H heads of D) at column q_off,
-// k (G heads of D) at k_off and v (G heads of E) at v_off. The first `rot` dimensions of every q and k head are rotated
-// by the row's position (pairs (i, i + rot/2) with pairing 0, (2i, 2i + 1) with pairing 1; the rest passes); then, if
+// k (G heads of D) at k_off and v (G heads of E) at v_off. The `rot` dimensions from `rot_off` on of every q and k head are
+// rotated by the row's position (pairs (i, i + rot/2) with pairing 0, (2i, 2i + 1) with pairing 1; the rest passes); then, if
 // asked, the head is divided by its root mean square over D (eps inside the root). q goes to q_out [T][H * D], k and v
 // to the token's page slot (planes [page][G][page_size][D] and [...][E]). All of it is 32-bit and rounded once.
 // No slot map (a layer that reads another layer's cache): q alone. A warp works on a head at a time.
@@ -606,8 +606,8 @@ template <typename TQ>
 __global__ void __launch_bounds__(256) rope_norm_store_kernel(const float* __restrict__ proj, long ld, int q_off, int k_off,
                                                               int v_off, const int* __restrict__ pos,
                                                               const int* __restrict__ slot_map,
-                                                              const float2* __restrict__ table, int rot, int pairing,
-                                                              int unit_norm, float eps, TQ* __restrict__ q_out,
+                                                              const float2* __restrict__ table, int rot, int rot_off,
+                                                              int pairing, int unit_norm, float eps, TQ* __restrict__ q_out,
                                                               TQ* __restrict__ kc, TQ* __restrict__ vc, int H, int G, int D,
                                                               int E, int page_size) {
   extern __shared__ float rn_sh[];      // [8 warps][D]
@@ -626,7 +626,7 @@ __global__ void __launch_bounds__(256) rope_norm_store_kernel(const float* __res
     __syncwarp();
     float ss = 0.f;
     for (int i = lane; i < half; i += 32) {
-      const int a = pairing ? 2 * i : i, b = pairing ? 2 * i + 1 : i + half;
+      const int a = rot_off + (pairing ? 2 * i : i), b = rot_off + (pairing ? 2 * i + 1 : i + half);
       const float u = buf[a], v = buf[b];
       const float2 c = cs[i];
       const float ru = __fsub_rn(__fmul_rn(u, c.x), __fmul_rn(v, c.y)), rv = __fadd_rn(__fmul_rn(v, c.x), __fmul_rn(u, c.y));
@@ -651,17 +651,17 @@ __global__ void __launch_bounds__(256) rope_norm_store_kernel(const float* __res
 }
 
 HB_EXPORT int hb_rope_norm_store(const float* proj, long ld, int q_off, int k_off, int v_off, const int* pos,
-                                 const int* slot_map, const void* table, int rot, int pairing, int unit_norm, float eps,
-                                 void* q_out, void* kc, void* vc, int q_dt, int T, int H, int G, int D, int E, int page_size,
+                                 const int* slot_map, const void* table, int rot, int rot_off, int pairing, int unit_norm,
+                                 float eps, void* q_out, void* kc, void* vc, int q_dt, int T, int H, int G, int D, int E, int page_size,
                                  cudaStream_t s) {
   if (T <= 0) return 0;
-  if (rot < 0 || rot > D || (rot & 1)) HB_FAIL("hb_rope_norm_store: %d rotated dimensions of a head of %d", rot, D);
+  if (rot < 0 || rot_off < 0 || rot_off + rot > D || (rot & 1)) HB_FAIL("hb_rope_norm_store: %d rotated dimensions from %d on of a head of %d", rot, rot_off, D);
   if (slot_map && (!kc || !vc || G <= 0 || E <= 0 || page_size <= 0)) HB_FAIL("hb_rope_norm_store: a slot map without caches or sizes");
   const size_t smem = (size_t)8 * D * sizeof(float);
   if (smem > 48 * 1024) HB_FAIL("hb_rope_norm_store: heads of %d are too wide", D);
   HB_DISPATCH_1(q_dt, "hb_rope_norm_store",
                 (hb_launch(rope_norm_store_kernel<TA>, T, 256, smem, s, proj, ld, q_off, k_off, v_off, pos, slot_map,
-                           (const float2*)table, rot, pairing, unit_norm, eps, (TA*)q_out, (TA*)kc, (TA*)vc, H, G, D, E,
+                           (const float2*)table, rot, rot_off, pairing, unit_norm, eps, (TA*)q_out, (TA*)kc, (TA*)vc, H, G, D, E,
                            page_size)));
   HB_CHECK_LAUNCH("hb_rope_norm_store");
   return 0;

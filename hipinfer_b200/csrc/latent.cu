@@ -71,12 +71,19 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
                                                                   long o_head, int T, int K, int N,
                                                                   const float* __restrict__ gate, long ld_gate, int gate_off,
                                                                   int tail, int rot, const int* __restrict__ pos,
-                                                                  const float2* __restrict__ table) {
+                                                                  const float2* __restrict__ table,
+                                                                  const int* __restrict__ row_req,
+                                                                  const int* __restrict__ q_len, int row_limit) {
   extern __shared__ float hl_a[];      // [HL_TM][K + tail]
   hb_pdl_launch();
   hb_pdl_wait();
   const int h = blockIdx.y, t0 = blockIdx.z * HL_TM, n = blockIdx.x * HL_THREADS + threadIdx.x;
   const int KT_ = K + tail, rows = min(HL_TM, T - t0);
+  // rows of requests that bring row_limit rows or more belong to another path: a block all of whose rows do is idle
+  unsigned skip = 0;
+  if (q_len)
+    for (int r = 0; r < rows; r++) skip |= (q_len[row_req[t0 + r]] >= row_limit ? 1u : 0u) << r;
+  if (q_len && skip == (1u << rows) - 1u) return;
   for (int i = threadIdx.x; i < rows * KT_; i += HL_THREADS) {
     const int r = i / KT_, k = i - r * KT_;
     hl_a[r * KT_ + k] = a[(size_t)(t0 + r) * lda + (size_t)h * a_head + k];
@@ -95,6 +102,7 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
 #pragma unroll
     for (int r = 0; r < HL_TM; r++) {
       if (r >= rows) break;
+      if (skip >> r & 1) continue;
       float o = acc[r];
       if (gate) o *= 1.f / (1.f + expf(-gate[(size_t)(t0 + r) * ld_gate + gate_off + (size_t)h * N + n]));
       out[(size_t)(t0 + r) * ldo + (size_t)h * o_head + n] = hb_from_float<TO>(o);
@@ -102,6 +110,7 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
   } else if (n < N + tail) {
     const int j = n - N, half = rot >> 1;
     for (int r = 0; r < rows; r++) {
+      if (skip >> r & 1) continue;
       const float* src = hl_a + r * KT_ + K;
       float y = src[j];
       if (j < rot) {
@@ -119,7 +128,8 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
 // outputs at column h * o_head.
 HB_EXPORT int hb_heads_linear(const float* a, long lda, long a_head, const void* wt, int w_dt, void* out, int o_dt, long ldo,
                               long o_head, int T, int H, int K, int N, const float* gate, long ld_gate, int gate_off, int tail,
-                              int rot, const int* pos, const void* table, cudaStream_t s) {
+                              int rot, const int* pos, const void* table, const int* row_req, const int* q_len, int row_limit,
+                              cudaStream_t s) {
   if (T <= 0 || H <= 0) return 0;
   if (tail && (!pos || !table || rot > tail || (rot & 1))) HB_FAIL("hb_heads_linear: a rotated tail needs positions and a table");
   const size_t smem = (size_t)HL_TM * (K + tail) * sizeof(float);
@@ -131,10 +141,36 @@ HB_EXPORT int hb_heads_linear(const float* a, long lda, long a_head, const void*
     auto kern = heads_linear_kernel<TW, TO>;                                                                    \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
     hb_launch(kern, grid, dim3(HL_THREADS), smem, s, a, lda, a_head, (const TW*)wt, (TO*)out, ldo, o_head, T, K, N, gate,  \
-              ld_gate, gate_off, tail, rot, pos, (const float2*)table);                                         \
+              ld_gate, gate_off, tail, rot, pos, (const float2*)table, row_req, q_len, row_limit);              \
   } while (0)
   HB_DISPATCH_2(w_dt, o_dt, "hb_heads_linear", HL_LAUNCH(TA, TB));
 #undef HL_LAUNCH
   HB_CHECK_LAUNCH("hb_heads_linear");
+  return 0;
+}
+
+// The rows of one request's tokens [0, n) of a cache plane with one head ([page][1][page_size][W]) copied, in the
+// order of their positions, into a contiguous buffer [n][W]: the input of a product over a request's whole context.
+template <typename TC>
+__global__ void __launch_bounds__(256) gather_rows_kernel(const TC* __restrict__ plane, const int* __restrict__ table,
+                                                          TC* __restrict__ dst, int n, int W, int page_size) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int vec = 16 / sizeof(TC), cw = W / vec;
+  for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < (long)n * cw; i += (long)gridDim.x * 256) {
+    const int t = (int)(i / cw), c = (int)(i - (long)t * cw);
+    const size_t row = (size_t)table[t / page_size] * page_size + t % page_size;
+    ((uint4*)(dst + (size_t)t * W))[c] = ((const uint4*)(plane + row * W))[c];
+  }
+}
+
+HB_EXPORT int hb_gather_rows(const void* plane, int dt, const int* table, void* dst, int n, int W, int page_size, cudaStream_t s) {
+  if (n <= 0) return 0;
+  const int esz = dt == HB_F32 ? 4 : 2;
+  if ((W * esz) % 16 || (((uintptr_t)plane | (uintptr_t)dst) & 15)) HB_FAIL("hb_gather_rows: rows of %d elements are no whole 16-byte chunks", W);
+  const long chunks = (long)n * (W * esz / 16);
+  const int blocks = (int)((chunks + 255) / 256 < 2048 ? (chunks + 255) / 256 : 2048);
+  HB_DISPATCH_1(dt, "hb_gather_rows", (hb_launch(gather_rows_kernel<TA>, blocks, 256, 0, s, (const TA*)plane, table, (TA*)dst, n, W, page_size)));
+  HB_CHECK_LAUNCH("hb_gather_rows");
   return 0;
 }

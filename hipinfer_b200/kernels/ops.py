@@ -35,7 +35,7 @@ _SIGS = {
         "hb_embed_pos": [_p, _p, _i, _p, _p, _p, _i, _i, _f, _p],
         "hb_layernorm": [_p, _p, _p, _i, _p, _i, _p, _i, _i, _f, _p],
         "hb_gated_act": [_p, _i, _l, _p, _i, _l, _i, _i, _i, _i, _p],
-        "hb_rope_norm_store": [_p, _l, _i, _i, _i, _p, _p, _p, _i, _i, _i, _f, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+        "hb_rope_norm_store": [_p, _l, _i, _i, _i, _p, _p, _p, _i, _i, _i, _i, _f, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
         "hb_polynorm": [_p, _l, _p, _i, _l, _i, _i, _f, _f, _f, _f, _f, _p],
         "hb_scale_add": [_p, _p, _l, _p, _i, _i, _i, _p],
         "hb_bias_act": [_p, _l, _p, _i, _p, _i, _l, _i, _i, _i, _p],
@@ -46,7 +46,11 @@ _SIGS = {
         "hb_attn_masked": [_p, _i, _l, _p, _l, _p, _l, _i, _p, _i, _p, _p, _p, _p, _l, _i, _i, _p, _i, _l, _i, _i, _i, _i, _i,
                            _i, _i, _i, _i, _i, _f, _p, _i, _p, _l, _p, _i, _p],
         "hb_latent_prepare": [_p, _l, _i, _i, _i, _p, _p, _i, _p, _p, _p, _i, _f, _p, _p, _i, _i, _i, _i, _i, _i, _p],
-        "hb_heads_linear": [_p, _l, _l, _p, _i, _p, _i, _l, _l, _i, _i, _i, _i, _p, _l, _i, _i, _i, _p, _p, _p],
+        "hb_heads_linear": [_p, _l, _l, _p, _i, _p, _i, _l, _l, _i, _i, _i, _i, _p, _l, _i, _i, _i, _p, _p, _p, _p, _i, _p],
+        "hb_gather_rows": [_p, _i, _p, _p, _i, _i, _i, _p],
+        "hb_attn_masked_flash_supported": [_i, _i],
+        "hb_attn_masked_flash": [_p, _l, _p, _l, _l, _l, _p, _l, _l, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _l, _i, _i, _p,
+                                 _i, _l, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
         "hb_gla": [_p, _l, _i, _i, _i, _i, _p, _l, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _f, _p],
     },
     "mixers": {
@@ -742,9 +746,9 @@ PAIRINGS = {"half": 0, "interleaved": 1}
 def rope_norm_store(proj: torch.Tensor, offsets, positions: torch.Tensor, slot_map: Optional[torch.Tensor],
                     table: torch.Tensor, rot: int, pairing: str, unit_norm: bool, eps: float, q_out: torch.Tensor,
                     k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], n_heads: int, n_kv_heads: int,
-                    dim: int, vdim: int, page_size: int) -> torch.Tensor:
+                    dim: int, vdim: int, page_size: int, rot_off: int = 0) -> torch.Tensor:
     """From a float32 projection result whose rows hold q, k, v at the column `offsets` (q, k, v): q and k rotated on
-    their first `rot` dimensions (pairing "half": (i, i + rot/2); "interleaved": (2i, 2i + 1)) and, with unit_norm,
+    the `rot` dimensions from `rot_off` on (pairing "half": (i, i + rot/2); "interleaved": (2i, 2i + 1)) and, with unit_norm,
     divided by their root mean square over `dim`; q to q_out [T, n_heads * dim], k and v (vdim wide, raw) to their page
     slots. slot_map None: q alone."""
     _need_cuda(proj, positions, slot_map, table, q_out, k_cache, v_cache)
@@ -757,7 +761,7 @@ def rope_norm_store(proj: torch.Tensor, offsets, positions: torch.Tensor, slot_m
         assert k_cache.shape[-1] == dim and v_cache.shape[-1] == vdim
     q_off, k_off, v_off = (int(o) for o in offsets)
     _call("core", "hb_rope_norm_store", proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, positions.data_ptr(),
-          _ptr(slot_map), table.data_ptr(), int(rot), PAIRINGS[pairing], 1 if unit_norm else 0, float(eps), q_out.data_ptr(),
+          _ptr(slot_map), table.data_ptr(), int(rot), int(rot_off), PAIRINGS[pairing], 1 if unit_norm else 0, float(eps), q_out.data_ptr(),
           _ptr(k_cache) if slot_map is not None else None, _ptr(v_cache) if slot_map is not None else None, _dt(q_out), T,
           n_heads, n_kv_heads, dim, vdim, page_size, _stream())
     return q_out
@@ -770,8 +774,10 @@ MASKED_FLASH_MIN_ROWS = 16
 def attention_masked(q, k_cache, v_cache, batch, group: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
                      page_size: int, scale: float, mask: str = "causal", window: int = 0, keep_first: int = 0, chunk: int = 0,
                      sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_offset: int = 0,
-                     gate_per_head: bool = False, force_rows: bool = False) -> torch.Tensor:
-    """Attention of the step's rows over their requests' pages (csrc/attention_masked.cu): keys `dim` and values `vdim`
+                     gate_per_head: bool = False, force_rows: bool = False, row_limit: int = 0) -> torch.Tensor:
+    """Attention of the step's rows over their requests' pages (csrc/attention_masked.cu; requests that bring many rows:
+    csrc/attention_masked_flash.cu). With row_limit, rows of requests that bring that many rows or more are left alone (the
+    caller has another path for them). Keys `dim` and values `vdim`
     wide, each plane [page, kv head, page_size, width] with a width of its own (v_cache may be the key plane itself:
     the values are then its first `vdim` columns). mask "causal", "window" (the last `window` keys and the first
     `keep_first`) or "chunk" (the keys of the row's own chunk of `chunk` positions). sink: float32 [n_heads], joins the
@@ -794,6 +800,24 @@ def attention_masked(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
     lib.hb_attn_masked_counters.argtypes = [_i] * 5
     max_pos = int(getattr(batch, "max_pos", 0)) or int(bt.shape[1]) * page_size - 1
     m = MASKS[mask]
+    # requests that bring MASKED_FLASH_MIN_ROWS rows or more go to the tensor-core kernel (bfloat16, the sizes it takes),
+    # the other rows of the step to the row kernel; a decode-only step is the row kernel alone
+    from . import fast
+
+    kw, vw = k_cache.shape[-1], v_cache.shape[-1]
+    flash = (q.dtype == torch.bfloat16 and not fast.PLAIN_ONLY and not force_rows and v_cache is not k_cache
+             and getattr(batch, "max_q_len", 0) >= MASKED_FLASH_MIN_ROWS and masked_flash_supported(dim, vdim)
+             and kw % 8 == 0 and vw % 8 == 0 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+    if flash:
+        _call("seqmix", "hb_attn_masked_flash", q.data_ptr(), q.stride(0), k_cache.data_ptr(), n_kv_heads * page_size * kw,
+              page_size * kw, kw, v_cache.data_ptr(), n_kv_heads * page_size * vw, page_size * vw, vw, bt.data_ptr(), bt.stride(0),
+              batch.req_q_start.data_ptr(), batch.req_q_len.data_ptr(), batch.req_ctx_len.data_ptr(), 0, batch.n_requests,
+              batch.max_q_len, MASKED_FLASH_MIN_ROWS, _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+              int(gate_offset), (2 if gate_per_head else 1) if gate is not None else 0, out.data_ptr(), _dt(out), out.stride(0),
+              n_heads, n_kv_heads, dim, vdim, page_size, m, int(window), int(keep_first), int(chunk), float(scale), _stream())
+        if min(batch.h_q_len) >= MASKED_FLASH_MIN_ROWS:
+            return out
+    limit = int(row_limit) or (MASKED_FLASH_MIN_ROWS if flash else 0)
     n_ws = lib.hb_attn_masked_workspace(T, n_heads, n_kv_heads, dim, vdim, m, int(window), int(keep_first), int(chunk), max_pos)
     ws = arrived = None
     if n_ws:
@@ -805,8 +829,8 @@ def attention_masked(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
           v_cache.data_ptr(), v_cache.shape[-1], _dt(k_cache), bt.data_ptr(), bt.stride(0), batch.row_request.data_ptr(),
           batch.positions.data_ptr(), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, int(gate_offset),
           (2 if gate_per_head else 1) if gate is not None else 0, out.data_ptr(), _dt(out), out.stride(0), T, n_heads,
-          n_kv_heads, dim, vdim, page_size, m, int(window), int(keep_first), int(chunk), float(scale), None, 0, _ptr(ws),
-          n_ws, _ptr(arrived), max_pos, _stream())
+          n_kv_heads, dim, vdim, page_size, m, int(window), int(keep_first), int(chunk), float(scale),
+          batch.req_q_len.data_ptr() if limit else None, limit, _ptr(ws), n_ws, _ptr(arrived), max_pos, _stream())
     return out
 
 
@@ -831,10 +855,12 @@ def latent_prepare(proj: torch.Tensor, offsets, wq: torch.Tensor, wc: torch.Tens
 
 
 def heads_linear(a: torch.Tensor, a_head: int, wt: torch.Tensor, out: torch.Tensor, o_head: int, gate=None,
-                 gate_offset: int = 0, tail: int = 0, rot: int = 0, positions=None, table=None) -> torch.Tensor:
+                 gate_offset: int = 0, tail: int = 0, rot: int = 0, positions=None, table=None, batch=None,
+                 row_limit: int = 0) -> torch.Tensor:
     """out[t, h * o_head + n] = sum_k a[t, h * a_head + k] wt[h, k, n] for every head h (a float32, 32-bit sums),
     optionally times sigmoid(gate[t, gate_offset + h * N + n]); with `tail`, the tail columns behind a head's K inputs
-    are rotated on their first `rot` (pairs (2i, 2i + 1)) by the row's position and copied behind its N outputs."""
+    are rotated on their first `rot` (pairs (2i, 2i + 1)) by the row's position and copied behind its N outputs. With
+    `batch` and `row_limit`, rows of requests that bring row_limit rows or more are left alone (another path has them)."""
     _need_cuda(a, wt, out, gate, positions, table)
     _rows_contiguous(a, "heads_linear a")
     _rows_contiguous(out, "heads_linear out")
@@ -845,7 +871,57 @@ def heads_linear(a: torch.Tensor, a_head: int, wt: torch.Tensor, out: torch.Tens
         assert gate.dtype == torch.float32 and gate.stride(1) == 1
     _call("seqmix", "hb_heads_linear", a.data_ptr(), a.stride(0), int(a_head), wt.data_ptr(), _dt(wt), out.data_ptr(),
           _dt(out), out.stride(0), int(o_head), T, H, K, N, _ptr(gate), gate.stride(0) if gate is not None else 0,
-          int(gate_offset), int(tail), int(rot), _ptr(positions), _ptr(table), _stream())
+          int(gate_offset), int(tail), int(rot), _ptr(positions), _ptr(table),
+          batch.row_request.data_ptr() if row_limit else None, batch.req_q_len.data_ptr() if row_limit else None, int(row_limit),
+          _stream())
+    return out
+
+
+def gather_rows(plane: torch.Tensor, table: torch.Tensor, dst: torch.Tensor, n: int, page_size: int) -> torch.Tensor:
+    """dst[t] = the cache row of position t, t < n, of a plane with one head [page, 1, page_size, W] through one request's
+    block table (int32 on the device)."""
+    _need_cuda(plane, table, dst)
+    assert plane.is_contiguous() and dst.is_contiguous() and plane.shape[1] == 1 and dst.shape == (n, plane.shape[-1])
+    assert plane.dtype == dst.dtype and table.dtype == torch.int32 and table.stride(-1) == 1
+    _call("seqmix", "hb_gather_rows", plane.data_ptr(), _dt(plane), table.data_ptr(), dst.data_ptr(), int(n), plane.shape[-1],
+          page_size, _stream())
+    return dst
+
+
+def fast_kernels_on() -> bool:
+    """False when the plain kernels are asked for everywhere (HIPINFER_B200_PLAIN=1)."""
+    from . import fast
+
+    return not fast.PLAIN_ONLY
+
+
+_identity_tables = {}
+
+
+def _identity_table(device, n: int) -> torch.Tensor:
+    t = _identity_tables.get(device)
+    if t is None or t.numel() < n:
+        t = _identity_tables[device] = torch.arange(max(n, 4096), dtype=torch.int32, device=device)
+    return t
+
+
+def masked_flash_supported(dim: int, vdim: int) -> bool:
+    return _fn("seqmix", "hb_attn_masked_flash_supported")(int(dim), int(vdim)) == 1
+
+
+def attention_flash_tokens(q, keys, values, batch, request: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
+                           scale: float, gate=None, gate_offset: int = 0, gate_per_head: bool = False) -> torch.Tensor:
+    """Causal attention of the rows of ONE request of the batch (index `request`) over keys and values made for its whole
+    context in token-major buffers: keys [n, >= n_kv_heads * dim] and values [n, >= n_kv_heads * vdim] (views of wider
+    rows are fine), row t the token at position t. bfloat16; the tensor-core kernel of csrc/attention_masked_flash.cu."""
+    _need_cuda(q, keys, values, out, gate)
+    n = keys.shape[0]
+    assert q.dtype == keys.dtype == values.dtype == torch.bfloat16 and keys.stride(1) == values.stride(1) == 1
+    _call("seqmix", "hb_attn_masked_flash", q.data_ptr(), q.stride(0), keys.data_ptr(), keys.stride(0), dim, 0, values.data_ptr(),
+          values.stride(0), vdim, 0, _identity_table(q.device, n).data_ptr(), 0, batch.req_q_start.data_ptr(),
+          batch.req_q_len.data_ptr(), batch.req_ctx_len.data_ptr(), int(request), 1, int(batch.h_q_len[request]), 1, None,
+          _ptr(gate), gate.stride(0) if gate is not None else 0, int(gate_offset), (2 if gate_per_head else 1) if gate is not None else 0,
+          out.data_ptr(), _dt(out), out.stride(0), n_heads, n_kv_heads, dim, vdim, 1, 0, 0, 0, 0, float(scale), _stream())
     return out
 
 

@@ -14,6 +14,12 @@ the cache reads [c | kr] rows as keys and their first kv_rank columns as values,
 latent (csrc/latent.cu). Root mean squares, angles, scores, softmax and the gate are 32-bit; the query that enters
 attention and the gated heads are rounded once each, the summed latent stays 32-bit.
 
+A request that brings many rows (a prompt portion; bfloat16) takes the other way round, the one with fewer operations
+per (row, key) pair: its latents, context and portion, are gathered from the pages and turned into the keys
+[Wuk_h c | kr] and values Wuv_h c of every head by ONE tensor-core product (the weight matrix has kr's columns as an
+identity block), and its rows attend over them with queries [plain | rotated] on the tensor-core kernel of
+csrc/attention_masked_flash.cu, the gate in its epilogue. Both ways compute the same sums; they differ in rounding.
+
 params: hidden_size, heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, eps, rot_dims (default rot_dim), rot_base, and the
 tensor names dq, dq_norm, uq, dkv, dkv_norm, uk, uv, g, o (`<key>_name`).
 """
@@ -64,6 +70,17 @@ class LatentAttentionMixer(Mixer):
         self.wuk_t = t["uk"].reshape(H, self.dim, self.kv_rank).contiguous()                      # [h][d][r]
         self.wuv_t = t["uv"].reshape(H, self.vdim, self.kv_rank).transpose(1, 2).contiguous()     # [h][r][e]
         self.wq_norm, self.wc_norm = t["dq_norm"], t["dkv_norm"].to(t["dq_norm"].dtype)
+        # for portions: [keys of every head | values of every head] = [c | kr] @ w_kv^T in one product
+        self.w_kv = None
+        D, Dr, E, R = self.dim, self.rot_dim, self.vdim, self.kv_rank
+        if (self.ctx.dtype == torch.bfloat16 and t["uk"].dtype == torch.bfloat16 and t["uv"].dtype == torch.bfloat16
+                and ops.masked_flash_supported(D + Dr, E) and (R + Dr) % 8 == 0):
+            wk = torch.zeros(H, D + Dr, R + Dr, dtype=torch.bfloat16, device=t["uk"].device)
+            wk[:, :D, :R] = t["uk"].reshape(H, D, R)
+            wk[:, D:, R:] = torch.eye(Dr, dtype=torch.bfloat16, device=wk.device)
+            wv = torch.zeros(H * E, R + Dr, dtype=torch.bfloat16, device=wk.device)
+            wv[:, :R] = t["uv"]
+            self.w_kv = ops.Weight(torch.cat([wk.reshape(H * (D + Dr), R + Dr), wv], 0).contiguous())
 
     def weight_bytes(self):
         return (self.w_in.nbytes + self.w_uq.nbytes + self.wo.nbytes
@@ -85,14 +102,37 @@ class LatentAttentionMixer(Mixer):
                            Rq, R, Dr, self.ctx.page_size)
         q = torch.empty(T, H * (D + Dr), dtype=torch.float32, device=dev)
         ops.linear(cq, self.w_uq, q)
+        att = torch.empty(T, H * E, dtype=self.ctx.dtype, device=dev)
+        # requests that bring many rows: keys and values of their whole context from one product, tensor-core attention
+        many = [r for r in range(batch.n_requests) if batch.h_q_len[r] >= ops.MASKED_FLASH_MIN_ROWS] \
+            if self.w_kv is not None and ops.fast_kernels_on() else []
+        if many:
+            qb = torch.empty(T, H * (D + Dr), dtype=self.ctx.dtype, device=dev)
+            ops.rope_norm_store(q, (0, 0, 0), batch.positions, None, self.table, self.rot_dims, "interleaved", False, 0.0, qb,
+                                None, None, H, 1, D + Dr, E, self.ctx.page_size, rot_off=D)
+            for r in many:
+                n = batch.h_ctx_len[r] + batch.h_q_len[r]
+                rows = torch.empty(n, R + Dr, dtype=self.ctx.dtype, device=dev)
+                ops.gather_rows(ckr, batch.block_tables[cache.group][r], rows, n, self.ctx.page_size)
+                kv = torch.empty(n, H * (D + Dr + E), dtype=self.ctx.dtype, device=dev)
+                ops.linear(rows, self.w_kv, kv)
+                ops.attention_flash_tokens(qb, kv[:, :H * (D + Dr)], kv[:, H * (D + Dr):], batch, r, att, H, H, D + Dr, E,
+                                           self.scale, gate=proj, gate_offset=Rq + R + Dr)
+            planes.record(batch, "q", qb)
+            if len(many) == batch.n_requests:
+                planes.record(batch, "attention", att)
+                ops.linear(att, self.wo, x, accumulate=True)
+                return None
+        limit = ops.MASKED_FLASH_MIN_ROWS if many else 0
         qa = torch.empty(T, H * (R + Dr), dtype=self.ctx.dtype, device=dev)        # per head [Wuk^T q_plain | rotated part]
         ops.heads_linear(q, D + Dr, self.wuk_t, qa, R + Dr, tail=Dr, rot=self.rot_dims, positions=batch.positions,
-                         table=self.table)
+                         table=self.table, batch=batch, row_limit=limit)
         lat = torch.empty(T, H * R, dtype=torch.float32, device=dev)               # per head the softmax-weighted sum of c
-        ops.attention_masked(qa, ckr, ckr, batch, cache.group, lat, H, 1, R + Dr, R, self.ctx.page_size, self.scale, "causal")
-        att = torch.empty(T, H * E, dtype=self.ctx.dtype, device=dev)
-        ops.heads_linear(lat, R, self.wuv_t, att, E, gate=proj, gate_offset=Rq + R + Dr)
-        planes.record(batch, "q", qa)
+        ops.attention_masked(qa, ckr, ckr, batch, cache.group, lat, H, 1, R + Dr, R, self.ctx.page_size, self.scale, "causal",
+                             row_limit=limit)
+        ops.heads_linear(lat, R, self.wuv_t, att, E, gate=proj, gate_offset=Rq + R + Dr, batch=batch, row_limit=limit)
+        if not many:
+            planes.record(batch, "q", qa)
         planes.record(batch, "attention", att)
         ops.linear(att, self.wo, x, accumulate=True)
         return None

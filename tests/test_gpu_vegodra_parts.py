@@ -333,3 +333,46 @@ def test_a_decay_of_one_keeps_and_a_decay_of_zero_forgets():
             S = (S if keep else 0 * S) + k[t][:, None] * v[t][None, :]
             o = S.T @ q[t]
             close(out[t], o / o.pow(2).mean().sqrt() * 30.0, torch.float32, f"token {t}, z = {zval}")
+
+
+@pytest.mark.parametrize("case", [(6, 2, 64, 64, "chunk", 0, 0, 96, True, "head"), (8, 2, 128, 128, "chunk", 0, 0, 200, True, "element"),
+                                  (4, 4, 64, 48, "causal", 0, 0, 0, False, "element"), (4, 1, 32, 32, "window", 70, 5, 0, True, "head"),
+                                  (2, 2, 48, 32, "chunk", 0, 0, 64, False, "none")],
+                         ids=lambda c: f"{c[4]}{c[7] or c[5] or ''}-h{c[0]}g{c[1]}-d{c[2]}e{c[3]}")
+def test_masked_attention_portions_on_tensor_cores(case):
+    """Portions of 16 rows and more run on the tensor-core kernel, the other rows of the same step on the row kernel:
+    a portion behind a long context (its first rows look back into other chunks and pages), a portion from position 0
+    whose last tile is ragged, and two single rows."""
+    from hipinfer_b200.kernels import ops
+
+    H, G, D, E, mask, window, keep, chunk, has_sink, gate_kind = case
+    dtype, ps, scale = torch.bfloat16, 16, 1.7 / math.sqrt(D)
+    ctx, new = [300, 0, 77, 5], [150, 83, 1, 1]
+    lens = [c + n for c, n in zip(ctx, new)]
+    keys = [rnd(n, G, D, seed=10 + r) for r, n in enumerate(lens)]
+    vals = [rnd(n, G, E, seed=20 + r) for r, n in enumerate(lens)]
+    kc, vc, bt = _paged(keys, vals, ps, dtype, seed=3)
+    rows = [(r, p) for r in range(4) for p in range(ctx[r], lens[r])]
+    T = len(rows)
+    q = rnd(T, H * D, seed=5)
+    sink = rnd(H, seed=6) * 2 if has_sink else None
+    n_gate = {"none": 0, "head": H, "element": H * E}[gate_kind]
+    gate = rnd(T, 8 + n_gate, seed=7) * 2 if n_gate else None
+    starts = [sum(new[:r]) for r in range(4)]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    batch = SimpleNamespace(block_tables=[bt], row_request=i32([r for r, _ in rows]), positions=i32([p for _, p in rows]),
+                            max_pos=max(lens) - 1, n_requests=4, max_q_len=max(new), h_q_len=new, req_q_start=i32(starts),
+                            req_q_len=i32(new), req_ctx_len=i32(ctx))
+    out = torch.full((T, H * E), float("nan"), dtype=dtype, device=DEV)
+    ops.attention_masked(q.to(dtype).to(DEV), kc, vc, batch, 0, out, H, G, D, E, ps, scale, mask, window, keep, chunk,
+                         None if sink is None else sink.to(DEV), None if gate is None else gate.to(DEV), 8, gate_kind == "head")
+    rows_only = torch.empty_like(out)
+    ops.attention_masked(q.to(dtype).to(DEV), kc, vc, batch, 0, rows_only, H, G, D, E, ps, scale, mask, window, keep, chunk,
+                         None if sink is None else sink.to(DEV), None if gate is None else gate.to(DEV), 8, gate_kind == "head",
+                         force_rows=True)
+    for t, (r, p) in enumerate(rows):
+        want = _attend_plain(q[t].to(dtype).double().view(H, D), keys[r].to(dtype).double(), vals[r].to(dtype).double(), p, H, G, scale,
+                             mask, window, keep, chunk, None if sink is None else sink.double(),
+                             None if gate is None else gate[t, 8:].double(), gate_kind == "head")
+        close(out[t], want, dtype, f"row {t} (request {r}, position {p})")
+        close(rows_only[t], want, dtype, f"row kernel, row {t}")
