@@ -462,6 +462,39 @@ def design_configs(size: dict, window: int):
     return torirax, llama
 
 
+def vegodra_configs(size: dict, window: int):
+    """(Vegodra config, Llama config) of equal width, depth, head counts and feed-forward width. Vegodra's layers cycle
+    latent attention, gated linear attention, latent attention, chunked attention with a sink (chunks of `window`
+    positions; every second one reads the cache of the one before it); every layer has the feed-forward. The latent
+    layers keep a latent of 4 x head_dim and a rotated part of head_dim / 2 per token; their heads have head_dim plain
+    and head_dim / 2 rotated query/key dimensions and values of head_dim."""
+    W, L, H, G, D = size["width"], size["layers"], size["heads"], size["kv"], size["head_dim"]
+    layers, last_owner, n_attn = [], None, 0
+    ff = dict(kind="dense", ff=size["ff"])
+    for i in range(L):
+        if i % 4 in (0, 2):
+            m = dict(heads=H, dim=D, rot_dim=D // 2, vdim=D, q_rank=12 * D, kv_rank=4 * D, scale=(D + D // 2) ** -0.5,
+                     rot=dict(base=10000.0, dims=D // 2))
+            layers.append(dict(type="latent_attention", mixer=m, mlp=ff))
+        elif i % 4 == 1:
+            layers.append(dict(type="gla", mixer=dict(heads=H, dim=D, vdim=D, tau=16.0, decay_rank=64), mlp=ff))
+        else:
+            m = dict(heads=H, kv_heads=G, dim=D, vdim=D, scale=0.125, rot=dict(base=1000000.0, dims=D // 2), mask=dict(size=window))
+            if n_attn % 2 == 1:
+                m["kv_from"] = last_owner
+            else:
+                last_owner = i
+            n_attn += 1
+            layers.append(dict(type="attention", mixer=m, mlp=ff))
+    vegodra = dict(architecture="Vegodra", vocab=size["vocab"], width=W, max_positions=CONTEXT_LEN, norm=dict(eps=1e-5), layers=layers)
+    llama = dict(MODEL, vocab_size=size["vocab"], hidden_size=W, intermediate_size=size["ff"], num_hidden_layers=L,
+                 num_attention_heads=H, num_key_value_heads=G, head_dim=D, tie_word_embeddings=False)
+    return vegodra, llama
+
+
+DESIGNS = {"torirax": design_configs, "vegodra": vegodra_configs}
+
+
 def kernel_table(one, reps: int = 3):
     """{kernel name: (launches, microseconds)} of one call of `one` (the middle of `reps` profiled calls)."""
     import json as _json
@@ -503,8 +536,8 @@ def kernel_table(one, reps: int = 3):
 
 
 def design_bench(a) -> int:
-    """Prefill and decode throughput of the Torirax design and of the Llama decoder at equal layer sizes, with each
-    step's kernels by name; one JSON line. The default run of this file is untouched by this option."""
+    """Prefill and decode throughput of the chosen design (Torirax or Vegodra) and of the Llama decoder at equal layer
+    sizes, with each step's kernels by name; one JSON line. The default run of this file is untouched by this option."""
     import torch
 
     from hipinfer_b200 import Engine
@@ -513,7 +546,7 @@ def design_bench(a) -> int:
 
     global PROMPT_LEN, PREFILL_TOKENS
     PROMPT_LEN, PREFILL_TOKENS = a.prompt, a.prefill_tokens
-    out = {"design": "torirax", "beside": "llama", "dtype": "bf16", "data": "synthetic: random token ids, random weights",
+    out = {"design": a.design, "beside": "llama", "dtype": "bf16", "data": "synthetic: random token ids, random weights",
            "prompt": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS, "window": a.window, "sizes": {}}
     clocks = ClockSampler().start()
     batches = [1, 8, 64]
@@ -524,7 +557,7 @@ def design_bench(a) -> int:
             size["layers"] = a.layers
         MODEL["vocab_size"] = size["vocab"]
         res = {}
-        for which, cfg in zip(("torirax", "llama"), design_configs(size, a.window)):
+        for which, cfg in zip((a.design, "llama"), DESIGNS[a.design](size, a.window)):
             pages_per_seq = -(-(PROMPT_LEN + a.steps + a.warmup + 16 + 4 * PAGE) // PAGE)
             eng = Engine(config=cfg, random_weights=0, std=0.02, dtype="bfloat16", max_batch=max(batches), max_seq=CONTEXT_LEN,
                          max_prefill=max(PREFILL_TOKENS, PROMPT_LEN), page_size=PAGE,
@@ -647,11 +680,11 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 decode points")
     ap.add_argument("--breakdown", action="store_true", help="print per-kernel times of a decode step and exit")
     ap.add_argument("--prefill", action="store_true", help="with --breakdown: the prefill step instead of a decode step")
-    ap.add_argument("--design", default=None, choices=["torirax"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="prefill and decode of this design beside the Llama decoder at equal layer sizes (see --sizes); "
                          "the default run is not changed by it")
     ap.add_argument("--sizes", default="1b", help="with --design: layer sizes, of " + ", ".join(sorted(DESIGN_SIZES)) + " (commas between)")
-    ap.add_argument("--window", type=int, default=1024, help="with --design: the attention window (the first 4 tokens are kept)")
+    ap.add_argument("--window", type=int, default=1024, help="with --design: the attention window (torirax: the first 4 tokens are kept) or chunk size (vegodra)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)

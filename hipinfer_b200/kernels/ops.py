@@ -49,6 +49,9 @@ _SIGS = {
         "hb_heads_linear": [_p, _l, _l, _p, _i, _p, _i, _l, _l, _i, _i, _i, _i, _p, _l, _i, _i, _i, _p, _p, _p, _p, _i, _p],
         "hb_gather_rows": [_p, _i, _p, _p, _i, _i, _i, _p],
         "hb_attn_masked_flash_supported": [_i, _i],
+        "hb_attn_masked_heads_supported": [_i, _i, _i, _i, _i],
+        "hb_attn_masked_heads": [_p, _l, _p, _l, _l, _l, _p, _l, _l, _l, _i, _p, _i, _p, _p, _p, _p, _l, _i, _i, _p, _i, _l, _i, _i,
+                                 _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _l, _p, _i, _p],
         "hb_attn_masked_flash": [_p, _l, _p, _l, _l, _l, _p, _l, _l, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _l, _i, _i, _p,
                                  _i, _l, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
         "hb_gla": [_p, _l, _i, _i, _i, _i, _p, _l, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _f, _p],
@@ -774,7 +777,8 @@ MASKED_FLASH_MIN_ROWS = 16
 def attention_masked(q, k_cache, v_cache, batch, group: int, out, n_heads: int, n_kv_heads: int, dim: int, vdim: int,
                      page_size: int, scale: float, mask: str = "causal", window: int = 0, keep_first: int = 0, chunk: int = 0,
                      sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_offset: int = 0,
-                     gate_per_head: bool = False, force_rows: bool = False, row_limit: int = 0) -> torch.Tensor:
+                     gate_per_head: bool = False, force_rows: bool = False, row_limit: int = 0,
+                     force_plain: bool = False) -> torch.Tensor:
     """Attention of the step's rows over their requests' pages (csrc/attention_masked.cu; requests that bring many rows:
     csrc/attention_masked_flash.cu). With row_limit, rows of requests that bring that many rows or more are left alone (the
     caller has another path for them). Keys `dim` and values `vdim`
@@ -805,7 +809,7 @@ def attention_masked(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
     from . import fast
 
     kw, vw = k_cache.shape[-1], v_cache.shape[-1]
-    flash = (q.dtype == torch.bfloat16 and not fast.PLAIN_ONLY and not force_rows and v_cache is not k_cache
+    flash = (q.dtype == torch.bfloat16 and not fast.PLAIN_ONLY and not force_rows and not force_plain and v_cache is not k_cache
              and getattr(batch, "max_q_len", 0) >= MASKED_FLASH_MIN_ROWS and masked_flash_supported(dim, vdim)
              and kw % 8 == 0 and vw % 8 == 0 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
     if flash:
@@ -818,6 +822,25 @@ def attention_masked(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
         if min(batch.h_q_len) >= MASKED_FLASH_MIN_ROWS:
             return out
     limit = int(row_limit) or (MASKED_FLASH_MIN_ROWS if flash else 0)
+    alias = v_cache is k_cache
+    if (q.dtype == torch.bfloat16 and not fast.PLAIN_ONLY and not force_plain and kw % 8 == 0 and vw % 8 == 0
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+            and _fn("seqmix", "hb_attn_masked_heads_supported")(n_heads, n_kv_heads, dim, vdim, 1 if alias else 0) == 1):
+        # the heads of a kv head as the rows of warp MMA tiles: a key tile is read once for all of them
+        lib.hb_attn_masked_heads_workspace.restype = C.c_long
+        lib.hb_attn_masked_heads_workspace.argtypes = [_i] * 9
+        lib.hb_attn_masked_heads_counters.argtypes = [_i] * 3
+        n_ws = lib.hb_attn_masked_heads_workspace(T, n_heads, n_kv_heads, vdim, m, int(window), int(keep_first), int(chunk), max_pos)
+        ws = torch.empty(n_ws, dtype=torch.float32, device=q.device) if n_ws else None
+        arrived = fast._decode_counters(q.device, lib.hb_attn_masked_heads_counters(T, n_heads, n_kv_heads)) if n_ws else None
+        _call("seqmix", "hb_attn_masked_heads", q.data_ptr(), q.stride(0), k_cache.data_ptr(), n_kv_heads * page_size * kw,
+              page_size * kw, kw, v_cache.data_ptr(), n_kv_heads * page_size * vw, page_size * vw, vw, 1 if alias else 0,
+              bt.data_ptr(), bt.stride(0), batch.row_request.data_ptr(), batch.positions.data_ptr(), _ptr(sink), _ptr(gate),
+              gate.stride(0) if gate is not None else 0, int(gate_offset), (2 if gate_per_head else 1) if gate is not None else 0,
+              out.data_ptr(), _dt(out), out.stride(0), T, n_heads, n_kv_heads, dim, vdim, page_size, m, int(window),
+              int(keep_first), int(chunk), float(scale), batch.req_q_len.data_ptr() if limit else None, limit, _ptr(ws), n_ws,
+              _ptr(arrived), max_pos, _stream())
+        return out
     n_ws = lib.hb_attn_masked_workspace(T, n_heads, n_kv_heads, dim, vdim, m, int(window), int(keep_first), int(chunk), max_pos)
     ws = arrived = None
     if n_ws:
