@@ -80,28 +80,37 @@ __global__ void __launch_bounds__(FM_THREADS) attn_masked_flash_kernel(FlashMask
   const int n_tiles = (last_keep_tile + 1) + (p_last / FM_KEYS - first_win_tile + 1);
   auto tile_at = [&](int i) { return i <= last_keep_tile ? i : first_win_tile + (i - (last_keep_tile + 1)); };
 
-  auto load_tile = [&](int buf, int tile) {
-    const int k0 = tile * FM_KEYS;
+  // Where a tile's 64 keys lie (element offsets of their key and value rows, -1: not wanted or its page given back) is
+  // looked up once a tile, by one thread a key, a tile before the copies that use it are issued: the copies themselves
+  // then wait for no load.
+  __shared__ long kofs[2][FM_KEYS], vofs[2][FM_KEYS];
+  auto locate = [&](int slot, int tile) {
+    if (tid < FM_KEYS) {
+      const int kp = tile * FM_KEYS + tid;
+      const bool want = kp <= p_last && (kp >= lo_first || kp < keep_last);
+      const int page = want ? table[kp / ps] : -1;
+      const int off = kp % ps;
+      kofs[slot][tid] = page >= 0 ? (long)page * A.k_page + (long)g * A.k_head + (long)off * A.k_row : -1;
+      vofs[slot][tid] = page >= 0 ? (long)page * A.v_page + (long)g * A.v_head + (long)off * A.v_row : -1;
+    }
+  };
+  auto load_tile = [&](int buf, int slot) {
     __nv_bfloat16* kd = Ks + buf * FM_KEYS * KP;
     __nv_bfloat16* vd = Vs + buf * FM_KEYS * VP;
     constexpr int CK = D / 8, CV = E / 8;
     for (int i = tid; i < FM_KEYS * (CK + CV); i += FM_THREADS) {
-      const int kr = i / (CK + CV), c = i - kr * (CK + CV), kp = k0 + kr;
+      const int kr = i / (CK + CV), c = i - kr * (CK + CV);
       __nv_bfloat16* dst = c < CK ? kd + kr * KP + c * 8 : vd + kr * VP + (c - CK) * 8;
-      const bool want = kp <= p_last && (kp >= lo_first || kp < keep_last);
-      const int page = want ? table[kp / ps] : -1;
-      if (page >= 0) {
-        const int off = kp % ps;
-        const __nv_bfloat16* src = c < CK ? A.kc + (size_t)page * A.k_page + (size_t)g * A.k_head + (size_t)off * A.k_row + c * 8
-                                          : A.vc + (size_t)page * A.v_page + (size_t)g * A.v_head + (size_t)off * A.v_row + (c - CK) * 8;
-        fm_cp16((uint32_t)__cvta_generic_to_shared(dst), src);
-      } else {
-        *(uint4*)dst = make_uint4(0u, 0u, 0u, 0u);
-      }
+      const long o = c < CK ? kofs[slot][kr] : vofs[slot][kr];
+      if (o >= 0) fm_cp16((uint32_t)__cvta_generic_to_shared(dst), (c < CK ? A.kc + o + c * 8 : A.vc + o + (c - CK) * 8));
+      else *(uint4*)dst = make_uint4(0u, 0u, 0u, 0u);
     }
   };
 
-  load_tile(0, tile_at(0));
+  locate(0, tile_at(0));
+  if (n_tiles > 1) locate(1, tile_at(1));
+  __syncthreads();
+  load_tile(0, 0);
   fm_commit();
 
   // this thread's two rows (quad and quad + 8 of the warp's 16) and their query fragments
@@ -129,42 +138,61 @@ __global__ void __launch_bounds__(FM_THREADS) attn_masked_flash_kernel(FlashMask
   for (int n = 0; n < EN; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
+  // scores are kept in units of log 2 (scale * log2(e) folded into one factor): exp is then one exp2 an element
+  const float sl2 = A.scale * 1.4426950408889634f;
   for (int it = 0; it < n_tiles; it++) {
     const int buf = it & 1, k0 = tile_at(it) * FM_KEYS;
     if (it + 1 < n_tiles) {
-      load_tile(buf ^ 1, tile_at(it + 1));
+      load_tile(buf ^ 1, buf ^ 1);            // located an iteration ago; the barrier that ended it made that visible
       fm_commit();
       fm_wait<1>();
     } else {
       fm_wait<0>();
     }
     __syncthreads();
+    if (it + 2 < n_tiles) locate(buf, tile_at(it + 2));     // this slot's copies are issued; visible after the next barrier
     const __nv_bfloat16* kt = Ks + buf * FM_KEYS * KP;
     const __nv_bfloat16* vt = Vs + buf * FM_KEYS * VP;
     float s[8][4];
 #pragma unroll
     for (int j = 0; j < 8; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    // lane l gives the row of matrix l / 8: keys (l / 16) * 8 + l % 8 of a pair of key tiles, columns ((l / 8) & 1) * 8
+    const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(kt + ((lane >> 4) * 8 + (lane & 7)) * KP + ((lane >> 3) & 1) * 8);
 #pragma unroll
     for (int ks = 0; ks < DK; ks++) {
 #pragma unroll
-      for (int j = 0; j < 8; j++) {
-        const __nv_bfloat16* kp_ = kt + (j * 8 + quad) * KP + ks * 16 + qi * 2;
-        fm_mma(s[j], qf[ks], *(const uint32_t*)kp_, *(const uint32_t*)(kp_ + 8));
+      for (int j = 0; j < 8; j += 2) {
+        uint32_t b[4];
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(k_addr + (uint32_t)((j * 8 * KP + ks * 16) * 2)));
+        fm_mma(s[j], qf[ks], b[0], b[1]);
+        fm_mma(s[j + 1], qf[ks], b[2], b[3]);
       }
     }
     // scale, mask, this tile's maximum
     float mx_a = -INFINITY, mx_b = -INFINITY;
+    // a tile every key of which both rows see (the common case away from the diagonal and the mask's edge) needs no test
+    const bool whole = va && vb && k0 + FM_KEYS - 1 <= pa && k0 >= lo_b;
+    if (whole) {
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
+      for (int j = 0; j < 8; j++) {
+        s[j][0] *= sl2; s[j][1] *= sl2; s[j][2] *= sl2; s[j][3] *= sl2;
+        mx_a = fmaxf(mx_a, fmaxf(s[j][0], s[j][1]));
+        mx_b = fmaxf(mx_b, fmaxf(s[j][2], s[j][3]));
+      }
+    } else {
 #pragma unroll
-      for (int c = 0; c < 4; c++) {
-        const int key = k0 + j * 8 + qi * 2 + (c & 1);
-        const bool top = c < 2;
-        const int p = top ? pa : pb, lo = top ? lo_a : lo_b, keep = top ? keep_a : keep_b;
-        const bool vis = (top ? va : vb) && key <= p && (key >= lo || key < keep);
-        const float v = vis ? s[j][c] * A.scale : -INFINITY;
-        s[j][c] = v;
-        if (top) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+      for (int j = 0; j < 8; j++) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          const int key = k0 + j * 8 + qi * 2 + (c & 1);
+          const bool top = c < 2;
+          const int p = top ? pa : pb, lo = top ? lo_a : lo_b, keep = top ? keep_a : keep_b;
+          const bool vis = (top ? va : vb) && key <= p && (key >= lo || key < keep);
+          const float v = vis ? s[j][c] * sl2 : -INFINITY;
+          s[j][c] = v;
+          if (top) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+        }
       }
     }
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
@@ -172,16 +200,16 @@ __global__ void __launch_bounds__(FM_THREADS) attn_masked_flash_kernel(FlashMask
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
     const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-    const float al_a = mn_a == -INFINITY ? 1.f : expf(m_a - mn_a), al_b = mn_b == -INFINITY ? 1.f : expf(m_b - mn_b);
+    const float al_a = mn_a == -INFINITY ? 1.f : exp2f(m_a - mn_a), al_b = mn_b == -INFINITY ? 1.f : exp2f(m_b - mn_b);
     m_a = mn_a;
     m_b = mn_b;
     float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; j++) {
-      s[j][0] = mn_a == -INFINITY ? 0.f : expf(s[j][0] - mn_a);
-      s[j][1] = mn_a == -INFINITY ? 0.f : expf(s[j][1] - mn_a);
-      s[j][2] = mn_b == -INFINITY ? 0.f : expf(s[j][2] - mn_b);
-      s[j][3] = mn_b == -INFINITY ? 0.f : expf(s[j][3] - mn_b);
+      s[j][0] = mn_a == -INFINITY ? 0.f : exp2f(s[j][0] - mn_a);
+      s[j][1] = mn_a == -INFINITY ? 0.f : exp2f(s[j][1] - mn_a);
+      s[j][2] = mn_b == -INFINITY ? 0.f : exp2f(s[j][2] - mn_b);
+      s[j][3] = mn_b == -INFINITY ? 0.f : exp2f(s[j][3] - mn_b);
       sum_a += s[j][0] + s[j][1];
       sum_b += s[j][2] + s[j][3];
     }
@@ -197,12 +225,15 @@ __global__ void __launch_bounds__(FM_THREADS) attn_masked_flash_kernel(FlashMask
       pf[1] = fm_pack(s[2 * kk][2], s[2 * kk][3]);
       pf[2] = fm_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
       pf[3] = fm_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-      const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(vt + (kk * 16 + (lane & 15)) * VP);
+      // lane l gives the row of matrix l / 8: keys (l & 7) + ((l >> 3) & 1) * 8 of the 16, columns (l >> 4) * 8 of a pair of tiles
+      const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + (lane >> 4) * 8);
 #pragma unroll
-      for (int n = 0; n < EN; n++) {
-        uint32_t b0, b1;
-        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(vrow + n * 16));
-        fm_mma(o[n], pf, b0, b1);
+      for (int n = 0; n + 1 < EN; n += 2) {
+        uint32_t b[4];
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(vrow + n * 16));
+        fm_mma(o[n], pf, b[0], b[1]);
+        fm_mma(o[n + 1], pf, b[2], b[3]);
       }
     }
     __syncthreads();           // before the next iteration's copies overwrite the other buffer... and this one after it
@@ -214,12 +245,12 @@ __global__ void __launch_bounds__(FM_THREADS) attn_masked_flash_kernel(FlashMask
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
   float f_a = 1.f, f_b = 1.f;
   if (A.sink) {
-    const float sk = A.sink[h];
+    const float sk = A.sink[h] * 1.4426950408889634f;       // the maxima are in units of log 2
     const float m2a = fmaxf(m_a, sk), m2b = fmaxf(m_b, sk);
-    f_a = expf(m_a - m2a);
-    l_a = fmaf(l_a, f_a, expf(sk - m2a));
-    f_b = expf(m_b - m2b);
-    l_b = fmaf(l_b, f_b, expf(sk - m2b));
+    f_a = exp2f(m_a - m2a);
+    l_a = fmaf(l_a, f_a, exp2f(sk - m2a));
+    f_b = exp2f(m_b - m2b);
+    l_b = fmaf(l_b, f_b, exp2f(sk - m2b));
   }
   f_a = l_a > 0.f ? f_a / l_a : 0.f;
   f_b = l_b > 0.f ? f_b / l_b : 0.f;

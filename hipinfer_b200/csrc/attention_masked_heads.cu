@@ -29,7 +29,7 @@ struct HeadsArgs {
   int H, G, D, E, MT, page_size, mask, window, keep_first, chunk;
   float scale;
   const int* q_len; int row_limit;
-  float* part;                          // [T][G][ZT][splits][16 MT][E + 2]
+  float* part;                          // [T][G][ZT][splits][16 MT][E + 4]
   int* arrived;                         // [T][G][ZT]
   int splits;
 };
@@ -82,26 +82,34 @@ __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs
   const int i0 = split * HS_SPLIT_TILES, i1 = min(n_tiles, i0 + HS_SPLIT_TILES);
   const int* table = A.bt + (size_t)A.row_req[t] * A.bt_stride;
 
-  auto load_tile = [&](int buf, int tile) {
-    const int k0 = tile * HK, CK = D / 8, CV = A.alias ? 0 : E / 8;
+  // where a tile's 64 keys lie is looked up once a tile, by one thread a key, a tile before the copies that use it
+  __shared__ long kofs[2][HK], vofs[2][HK];
+  auto locate = [&](int slot, int tile) {
+    if (tid < HK) {
+      const int kp = tile * HK + tid;
+      const bool vis = kp <= p && (kp >= lo || kp < keep);
+      const int page = vis ? table[kp / ps] : -1;
+      const int off = kp % ps;
+      kofs[slot][tid] = page >= 0 ? (long)page * A.k_page + (long)g * A.k_head + (long)off * A.k_row : -1;
+      vofs[slot][tid] = page >= 0 ? (long)page * A.v_page + (long)g * A.v_head + (long)off * A.v_row : -1;
+    }
+  };
+  auto load_tile = [&](int buf, int slot) {
+    const int CK = D / 8, CV = A.alias ? 0 : E / 8;
     __nv_bfloat16* kd = Ks + buf * HK * KP;
     __nv_bfloat16* vd = Vs + buf * HK * VP;
     for (int i = tid; i < HK * (CK + CV); i += HS_THREADS) {
-      const int kr = i / (CK + CV), c = i - kr * (CK + CV), kp = k0 + kr;
+      const int kr = i / (CK + CV), c = i - kr * (CK + CV);
       __nv_bfloat16* dst = c < CK ? kd + kr * KP + c * 8 : vd + kr * VP + (c - CK) * 8;
-      const bool vis = kp <= p && (kp >= lo || kp < keep);
-      const int page = vis ? table[kp / ps] : -1;
-      if (page >= 0) {
-        const int off = kp % ps;
-        const __nv_bfloat16* src = c < CK ? A.kc + (size_t)page * A.k_page + (size_t)g * A.k_head + (size_t)off * A.k_row + c * 8
-                                          : A.vc + (size_t)page * A.v_page + (size_t)g * A.v_head + (size_t)off * A.v_row + (c - CK) * 8;
-        hs_cp16((uint32_t)__cvta_generic_to_shared(dst), src);
-      } else {
-        *(uint4*)dst = make_uint4(0u, 0u, 0u, 0u);
-      }
+      const long o = c < CK ? kofs[slot][kr] : vofs[slot][kr];
+      if (o >= 0) hs_cp16((uint32_t)__cvta_generic_to_shared(dst), (c < CK ? A.kc + o + c * 8 : A.vc + o + (c - CK) * 8));
+      else *(uint4*)dst = make_uint4(0u, 0u, 0u, 0u);
     }
   };
-  load_tile(0, hs_tile_at(i0, lo, keep));
+  locate(0, hs_tile_at(i0, lo, keep));
+  if (i0 + 1 < i1) locate(1, hs_tile_at(i0 + 1, lo, keep));
+  __syncthreads();
+  load_tile(0, 0);
   asm volatile("cp.async.commit_group;" ::: "memory");
   // the queries of the tile's heads (rows beyond the group's heads are zero)
   {
@@ -119,16 +127,19 @@ __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
   const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (mt * 16 + (lane & 15)) * KP + (lane >> 4) * 8);
 
+  // scores are kept in units of log 2 (scale * log2(e) folded into one factor): exp is then one exp2 an element
+  const float sl2 = A.scale * 1.4426950408889634f;
   for (int it = i0; it < i1; it++) {
     const int buf = (it - i0) & 1, k0 = hs_tile_at(it, lo, keep) * HK;
     if (it + 1 < i1) {
-      load_tile(buf ^ 1, hs_tile_at(it + 1, lo, keep));
+      load_tile(buf ^ 1, buf ^ 1);            // located an iteration ago (or before the loop)
       asm volatile("cp.async.commit_group;" ::: "memory");
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    if (it + 2 < i1) locate(buf, hs_tile_at(it + 2, lo, keep));
     const __nv_bfloat16* kt = Ks + buf * HK * KP;
     const __nv_bfloat16* vt = Vs + buf * HK * VP;
     float s[8][4];
@@ -156,7 +167,7 @@ __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs
       for (int c = 0; c < 4; c++) {
         const int key = k0 + j * 8 + qi * 2 + (c & 1);
         const bool vis = key <= p && (key >= lo || key < keep);
-        const float v = vis ? s[j][c] * A.scale : -INFINITY;
+        const float v = vis ? s[j][c] * sl2 : -INFINITY;
         s[j][c] = v;
         if (c < 2) mx = fmaxf(mx, v); else mx_b = fmaxf(mx_b, v);
       }
@@ -166,16 +177,16 @@ __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
     const float mn_a = fmaxf(m_a, mx), mn_b = fmaxf(m_b, mx_b);
-    const float al_a = mn_a == -INFINITY ? 1.f : expf(m_a - mn_a), al_b = mn_b == -INFINITY ? 1.f : expf(m_b - mn_b);
+    const float al_a = mn_a == -INFINITY ? 1.f : exp2f(m_a - mn_a), al_b = mn_b == -INFINITY ? 1.f : exp2f(m_b - mn_b);
     m_a = mn_a;
     m_b = mn_b;
     float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; j++) {
-      s[j][0] = mn_a == -INFINITY ? 0.f : expf(s[j][0] - mn_a);
-      s[j][1] = mn_a == -INFINITY ? 0.f : expf(s[j][1] - mn_a);
-      s[j][2] = mn_b == -INFINITY ? 0.f : expf(s[j][2] - mn_b);
-      s[j][3] = mn_b == -INFINITY ? 0.f : expf(s[j][3] - mn_b);
+      s[j][0] = mn_a == -INFINITY ? 0.f : exp2f(s[j][0] - mn_a);
+      s[j][1] = mn_a == -INFINITY ? 0.f : exp2f(s[j][1] - mn_a);
+      s[j][2] = mn_b == -INFINITY ? 0.f : exp2f(s[j][2] - mn_b);
+      s[j][3] = mn_b == -INFINITY ? 0.f : exp2f(s[j][3] - mn_b);
       sum_a += s[j][0] + s[j][1];
       sum_b += s[j][2] + s[j][3];
     }
@@ -211,7 +222,7 @@ __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs
   // the accumulators, maxima and sums go through memory: shared (one split) or the workspace (several)
   float* stage;
   const size_t slot = ((size_t)t * A.G + g) * ZT + z;
-  const int RS = E + 2;
+  const int RS = E + 4;                 // a row's sums, then its maximum and weight sum; rows stay 16-byte aligned
   if (n_splits_row > 1) stage = A.part + (slot * A.splits + split) * (size_t)MR * RS;
   else stage = (float*)hs_smem;                       // the tiles are done with
   __syncthreads();
@@ -244,27 +255,68 @@ __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs
     __syncthreads();
   }
   const size_t pstride = (size_t)MR * RS;
+  // every head's factor for each split (exp of the split's maximum against the row's, over the weight sum with the sink,
+  // times the head's gate) first, into shared memory behind the staged sums; then every (head, 4 columns) is one
+  // thread's sum over the splits, all loads independent of one another
+  float* wsp = (float*)hs_smem + (size_t)MR * RS;            // [nh][n_parts], n_parts <= 64 here
+  const bool use_table = n_parts <= 64;
+  if (use_table) {
+    for (int r = tid; r < nh; r += HS_THREADS) {
+      const size_t head = (size_t)g * HG + h0 + r;
+      float m = -INFINITY;
+      for (int sp = 0; sp < n_parts; sp++) m = fmaxf(m, all[sp * pstride + r * RS + E]);
+      float l = 0.f;
+      for (int sp = 0; sp < n_parts; sp++) l = fmaf(all[sp * pstride + r * RS + E + 1], exp2f(all[sp * pstride + r * RS + E] - m), l);
+      float f = 1.f;
+      if (A.sink) {
+        const float sk = A.sink[head] * 1.4426950408889634f, m2 = fmaxf(m, sk);     // the maxima are in units of log 2
+        f = exp2f(m - m2);
+        l = fmaf(l, f, exp2f(sk - m2));
+      }
+      f = l > 0.f ? f / l : 0.f;
+      if (A.gate_mode == 2) f *= 1.f / (1.f + expf(-A.gate[(size_t)t * A.ld_gate + A.gate_off + head]));
+      for (int sp = 0; sp < n_parts; sp++) wsp[r * n_parts + sp] = exp2f(all[sp * pstride + r * RS + E] - m) * f;
+    }
+    __syncthreads();
+    const int C4 = E / 4;
+    for (int i = tid; i < nh * C4; i += HS_THREADS) {
+      const int r = i / C4, e = (i - r * C4) * 4;
+      const size_t head = (size_t)g * HG + h0 + r;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+      for (int sp = 0; sp < n_parts; sp++) {
+        const float4 v = *(const float4*)(all + sp * pstride + r * RS + e);
+        const float w = wsp[r * n_parts + sp];
+        a.x = fmaf(v.x, w, a.x); a.y = fmaf(v.y, w, a.y); a.z = fmaf(v.z, w, a.z); a.w = fmaf(v.w, w, a.w);
+      }
+      if (A.gate_mode == 1) {
+        const float* gp = A.gate + (size_t)t * A.ld_gate + A.gate_off + head * E + e;
+        a.x *= 1.f / (1.f + expf(-gp[0])); a.y *= 1.f / (1.f + expf(-gp[1]));
+        a.z *= 1.f / (1.f + expf(-gp[2])); a.w *= 1.f / (1.f + expf(-gp[3]));
+      }
+      TO* op = (TO*)A.out + (size_t)t * A.ldo + head * E + e;
+      op[0] = hb_from_float<TO>(a.x); op[1] = hb_from_float<TO>(a.y); op[2] = hb_from_float<TO>(a.z); op[3] = hb_from_float<TO>(a.w);
+    }
+    return;
+  }
   for (int r = warp; r < nh; r += HS_THREADS / 32) {
     const size_t head = (size_t)g * HG + h0 + r;
     float m = -INFINITY;
     for (int sp = 0; sp < n_parts; sp++) m = fmaxf(m, all[sp * pstride + r * RS + E]);
     float l = 0.f;
-    for (int sp = 0; sp < n_parts; sp++) l = fmaf(all[sp * pstride + r * RS + E + 1], expf(all[sp * pstride + r * RS + E] - m), l);
-    // the sink joins the denominator: against the larger of the keys' maximum and the sink, f rescales the keys' share
+    for (int sp = 0; sp < n_parts; sp++) l = fmaf(all[sp * pstride + r * RS + E + 1], exp2f(all[sp * pstride + r * RS + E] - m), l);
     float f = 1.f;
     if (A.sink) {
-      const float sk = A.sink[head], m2 = fmaxf(m, sk);
-      f = expf(m - m2);
-      l = fmaf(l, f, expf(sk - m2));
+      const float sk = A.sink[head] * 1.4426950408889634f, m2 = fmaxf(m, sk);
+      f = exp2f(m - m2);
+      l = fmaf(l, f, exp2f(sk - m2));
     }
     f = l > 0.f ? f / l : 0.f;
     float gh = 1.f;
     if (A.gate_mode == 2) gh = 1.f / (1.f + expf(-A.gate[(size_t)t * A.ld_gate + A.gate_off + head]));
     for (int e = lane; e < E; e += 32) {
       float a = 0.f;
-      if (n_parts == 1) a = all[r * RS + e];
-      else
-        for (int sp = 0; sp < n_parts; sp++) a = fmaf(all[sp * pstride + r * RS + e], expf(all[sp * pstride + r * RS + E] - m), a);
+      for (int sp = 0; sp < n_parts; sp++) a = fmaf(all[sp * pstride + r * RS + e], exp2f(all[sp * pstride + r * RS + E] - m), a);
       a *= f;
       if (A.gate_mode == 1) a *= 1.f / (1.f + expf(-A.gate[(size_t)t * A.ld_gate + A.gate_off + head * E + e]));
       else if (A.gate_mode == 2) a *= gh;
@@ -276,7 +328,7 @@ __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs
 static int hs_mt(int HG) { return HG > 16 ? 2 : 1; }
 static size_t hs_smem_bytes(int MT, int D, int E, int alias) {
   size_t tiles = (size_t)(16 * MT) * (D + 8) * 2 + (size_t)2 * HK * (D + 8) * 2 + (alias ? 0 : (size_t)2 * HK * (E + 8) * 2);
-  size_t stage = (size_t)(16 * MT) * (E + 2) * 4;
+  size_t stage = (size_t)(16 * MT) * (E + 4) * 4 + (size_t)(16 * MT) * 64 * 4;   // one split's sums, and the splits' weights
   return tiles > stage ? tiles : stage;
 }
 static int hs_splits(int mask, int window, int keep_first, int chunk, int max_pos) {
@@ -309,7 +361,7 @@ HB_EXPORT long hb_attn_masked_heads_workspace(int T, int H, int G, int E, int ma
   const int HG = H / G, MT = hs_mt(HG), ZT = (HG + 16 * MT - 1) / (16 * MT);
   const int splits = hs_splits(mask, window, keep_first, chunk, max_pos);
   if (splits <= 1) return 0;
-  return (long)T * G * ZT * splits * 16 * MT * (E + 2);
+  return (long)T * G * ZT * splits * 16 * MT * (E + 4);
 }
 HB_EXPORT int hb_attn_masked_heads_counters(int T, int H, int G) {
   const int HG = H / G, MT = hs_mt(HG), ZT = (HG + 16 * MT - 1) / (16 * MT);
@@ -340,7 +392,7 @@ HB_EXPORT int hb_attn_masked_heads(const void* q, long ldq, const void* kc, long
   const int ZT = (HG + 16 * A.MT - 1) / (16 * A.MT);
   A.splits = hs_splits(mask, window, keep_first, chunk, max_pos);
   if (A.splits < 1) A.splits = 1;
-  if (A.splits > 1 && (!part || !arrived || n_part < (long)T * G * ZT * A.splits * 16 * A.MT * (E + 2)))
+  if (A.splits > 1 && (!part || !arrived || n_part < (long)T * G * ZT * A.splits * 16 * A.MT * (E + 4)))
     HB_FAIL("hb_attn_masked_heads: rows of up to %d key tiles need a workspace", A.splits * HS_SPLIT_TILES);
   if ((long)ZT * A.splits > 65535) HB_FAIL("hb_attn_masked_heads: the grid is too large");
   const size_t smem = hs_smem_bytes(A.MT, D, E, alias);

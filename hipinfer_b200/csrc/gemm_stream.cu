@@ -20,7 +20,8 @@
 
 HB_TL_DEFINE(stream)
 
-enum { ST_F32 = 0, ST_BF16 = 1, ST_ADD_F32 = 2, ST_SWIGLU_BF16 = 3, ST_SLICES = 4 };
+enum { ST_F32 = 0, ST_BF16 = 1, ST_ADD_F32 = 2, ST_SWIGLU_BF16 = 3, ST_SLICES = 4, ST_GEGLU_BF16 = 5 };   // 5: as 3 with the tanh form of GELU
+#define ST_IS_GLU(e) ((e) == ST_SWIGLU_BF16 || (e) == ST_GEGLU_BF16)
 constexpr int ST_ROWS = 128, ST_BK = 64, ST_W_BYTES = ST_ROWS * ST_BK * 2;
 
 // DEEP: the pipeline of a product that is not split along K (many column blocks): six stages,
@@ -35,9 +36,10 @@ template <int NT, bool DEEP> struct StreamCfg {
 
 __device__ __forceinline__ void stream_store(int epi, void* C, long ldc, int m, int n, int N, float v, float v_up, bool lower_half) {
   // lower_half: this column is a gate column (n % 32 < 16); v_up is the matching up column's value
-  if (epi == ST_SWIGLU_BF16) {
+  if (ST_IS_GLU(epi)) {
+    const float arg = epi == ST_GEGLU_BF16 ? 1.5957691216057308f * (v + 0.044715f * v * v * v) : v;   // gelu_tanh(v) = v sigmoid(2 sqrt(2/pi) (v + 0.044715 v^3))
     if (lower_half && n < N) ((__nv_bfloat16*)C)[(size_t)m * ldc + (n >> 5) * 16 + (n & 15)] =
-        __float2bfloat16_rn(v / (1.f + __expf(-v)) * v_up);
+        __float2bfloat16_rn(v / (1.f + __expf(-arg)) * v_up);
   } else if (n < N) {
     if (epi == ST_BF16) ((__nv_bfloat16*)C)[(size_t)m * ldc + n] = __float2bfloat16_rn(v);
     else if (epi == ST_ADD_F32) ((float*)C)[(size_t)m * ldc + n] += v;
@@ -167,7 +169,7 @@ __global__ void __launch_bounds__(192) gemm_stream_kernel(const __grid_constant_
   const size_t slice_stride = (size_t)NT * NP;
   for (int i = threadIdx.x; i < (ST_ROWS / 4) * M; i += 192) {
     const int m = i / (ST_ROWS / 4), nl = (i - m * (ST_ROWS / 4)) * 4, n = n0 + nl;
-    const bool gate = (nl & 16) == 0, swiglu = epi == ST_SWIGLU_BF16;
+    const bool gate = (nl & 16) == 0, swiglu = ST_IS_GLU(epi);
     if (n >= N || (swiglu && !gate)) continue;
     const float* p = ws + (size_t)m * NP + n;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = acc;
@@ -214,7 +216,7 @@ __global__ void __launch_bounds__(256) stream_reduce_kernel(const float* __restr
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long)M * per_row) return;
   const int m = (int)(idx / per_row), n = (int)(idx - (long)m * per_row) * 4;
-  const bool gate = (n & 16) == 0, swiglu = epi == ST_SWIGLU_BF16;
+  const bool gate = (n & 16) == 0, swiglu = ST_IS_GLU(epi);
   if (n >= N || (swiglu && !gate)) return;
   const size_t slice_stride = (size_t)NT * NP;
   const float* p = ws + (size_t)m * NP + n;
@@ -310,8 +312,8 @@ HB_EXPORT int hb_gemm_stream(const void* A, long lda, const void* W, long ldw, v
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) HB_FAIL("hb_gemm_stream: M = %d is beyond 64 rows", M);
   if (K <= 0 || (K & 7)) HB_FAIL("hb_gemm_stream: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
-  if (epi < 0 || epi > 4) HB_FAIL("hb_gemm_stream: unknown epilogue %d", epi);
-  if (epi == ST_SWIGLU_BF16 && (N & 31)) HB_FAIL("hb_gemm_stream: SwiGLU needs N = %d to be a multiple of 32", N);
+  if (epi < 0 || epi > 5) HB_FAIL("hb_gemm_stream: unknown epilogue %d", epi);
+  if (ST_IS_GLU(epi) && (N & 31)) HB_FAIL("hb_gemm_stream: a gated epilogue needs N = %d to be a multiple of 32", N);
   if (!status) HB_FAIL("hb_gemm_stream: no status word");
   int kslice, ksplit, n_blocks;
   long per_token;
@@ -343,7 +345,7 @@ HB_EXPORT int hb_gemm_stream(const void* A, long lda, const void* W, long ldw, v
 // Finish a product that was left as slices (epi 4): C per `epi` (0 to 3) from ws, for the same M, N, K.
 HB_EXPORT int hb_gemm_stream_finish(const float* ws, void* C, long ldc, int M, int N, int K, int epi, cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
-  if (epi < 0 || epi > 3) HB_FAIL("hb_gemm_stream_finish: unknown epilogue %d", epi);
+  if (epi < 0 || (epi > 3 && epi != ST_GEGLU_BF16)) HB_FAIL("hb_gemm_stream_finish: unknown epilogue %d", epi);
   int kslice, ksplit, n_blocks;
   long per_token;
   hb_gemm_stream_plan(N, K, &kslice, &ksplit, &per_token, &n_blocks);
@@ -389,7 +391,7 @@ HB_EXPORT int hb_gemm_stream_static(const void* A, long lda, const void* W, long
   if (M > 64) HB_FAIL("hb_gemm_stream_static: M = %d is beyond 64 rows", M);
   if (K <= 0 || (K & 7)) HB_FAIL("hb_gemm_stream_static: K = %d must be a positive multiple of 8", K);
   if (epi < 0 || epi > 3) HB_FAIL("hb_gemm_stream_static: unknown epilogue %d (0 to 3)", epi);
-  if (epi == ST_SWIGLU_BF16 && (N & 31)) HB_FAIL("hb_gemm_stream_static: SwiGLU needs N = %d to be a multiple of 32", N);
+  if (ST_IS_GLU(epi) && (N & 31)) HB_FAIL("hb_gemm_stream_static: a gated epilogue needs N = %d to be a multiple of 32", N);
   if (!status) HB_FAIL("hb_gemm_stream_static: no status word");
   int kslice, ksplit, n_blocks;
   long per_token;

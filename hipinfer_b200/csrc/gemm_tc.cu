@@ -16,7 +16,15 @@
 // drains and returns.
 #include "tc_common.cuh"
 
-enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3, EPI_ROPE_KV = 4 };
+enum { EPI_F32 = 0, EPI_BF16 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU_BF16 = 3, EPI_ROPE_KV = 4, EPI_GEGLU_BF16 = 5 };
+
+// The gated epilogues: act(gate) * up over 16-interleaved columns, act = silu (3) or the tanh form of GELU (5), which is
+// g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3)).
+#define EPI_IS_GLU(E) ((E) == EPI_SWIGLU_BF16 || (E) == EPI_GEGLU_BF16)
+template <int EPI> __device__ __forceinline__ float hb_glu_act(float g) {
+  if (EPI == EPI_GEGLU_BF16) return g / (1.f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + __expf(-g));
+}
 
 // EPI_ROPE_KV: the product is a q/k/v projection of heads of 64; the epilogue rotates the q and k heads (half-split
 // pairs (d, d + 32), the angles from a table of (cos, sin) per position) and writes q as bf16 [M, Hq * 64], k and v
@@ -52,7 +60,7 @@ template <int EPI>
 __device__ __forceinline__ void epilogue_store(const float* v, void* C, long ldc, int row, int col0, int M, int N) {
   // v: 32 consecutive columns col0.. of `row`
   if (row >= M) return;
-  if (EPI == EPI_SWIGLU_BF16) {
+  if (EPI_IS_GLU(EPI)) {
     // columns [0,16) gate, [16,32) up of outputs (col0/2) .. +15
     __nv_bfloat16* out = (__nv_bfloat16*)C + (size_t)row * ldc + (col0 >> 1);
     const int n_out = N >> 1, o0 = col0 >> 1;
@@ -60,7 +68,7 @@ __device__ __forceinline__ void epilogue_store(const float* v, void* C, long ldc
 #pragma unroll
     for (int j = 0; j < 16; j++) {
       const float g = v[j], u = v[16 + j];
-      r[j] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+      r[j] = __float2bfloat16_rn(hb_glu_act<EPI>(g) * u);
     }
     if (o0 + 16 <= n_out && ((ldc & 7) == 0)) {
       *(uint4*)(out) = *(const uint4*)(r);
@@ -137,19 +145,19 @@ __device__ __forceinline__ void rope_head_store(float* x1, float* x2, int head, 
 template <int EPI>
 __device__ __forceinline__ void ts_chunk(const float* v, int c, int n0, int N, int row0, uint8_t* boxes, int lane,
                                          const CUtensorMap* map_c) {
-  constexpr int PER = EPI == EPI_SWIGLU_BF16 ? 4 : EPI == EPI_BF16 ? 2 : 1;
+  constexpr int PER = EPI_IS_GLU(EPI) ? 4 : EPI == EPI_BF16 ? 2 : 1;
   uint8_t* box = boxes + ((c / PER) & 1) * 4096;
   if (c % PER == 0) {
     if (lane == 0) hb_tma_store_wait_read<1>();   // the store that last read this box is done with it
     __syncwarp();
   }
   const uint32_t b = hb_smem_u32(box) + lane * 128;
-  if constexpr (EPI == EPI_SWIGLU_BF16) {
+  if constexpr (EPI_IS_GLU(EPI)) {
     uint32_t r[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) {
       const float g0 = v[2 * j], g1 = v[2 * j + 1];
-      r[j] = hb_pack_bf16(g0 / (1.f + __expf(-g0)) * v[16 + 2 * j], g1 / (1.f + __expf(-g1)) * v[17 + 2 * j]);
+      r[j] = hb_pack_bf16(hb_glu_act<EPI>(g0) * v[16 + 2 * j], hb_glu_act<EPI>(g1) * v[17 + 2 * j]);
     }
 #pragma unroll
     for (int j = 0; j < 2; j++)
@@ -172,7 +180,7 @@ __device__ __forceinline__ void ts_chunk(const float* v, int c, int n0, int N, i
     __syncwarp();
     if (lane == 0) {
       // first column of the box in the output: accumulator column / 2 for SwiGLU
-      const int x = EPI == EPI_SWIGLU_BF16 ? (n0 >> 1) + (c / PER) * 64 : n0 + (c / PER) * (PER * 32);
+      const int x = EPI_IS_GLU(EPI) ? (n0 >> 1) + (c / PER) * 64 : n0 + (c / PER) * (PER * 32);
       if (EPI == EPI_ADD_F32) hb_tma_reduce_add_2d(map_c, box, x, row0);
       else hb_tma_store_2d(map_c, box, x, row0);
       hb_tma_store_commit();
@@ -548,7 +556,7 @@ static int launch_gemm_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C,
     }
   } else {
     if (HB_GEMM_TMA_STORE && !((uintptr_t)C & 15) && (ldc & 7) == 0) {   // bf16 [M, N] or [M, N / 2]: boxes of 32 rows x 64 columns
-      const uint64_t cols = EPI == EPI_SWIGLU_BF16 ? (uint64_t)N / 2 : (uint64_t)N;
+      const uint64_t cols = EPI_IS_GLU(EPI) ? (uint64_t)N / 2 : (uint64_t)N;
       if (hb_make_tensor_map_bf16(&mc, C, (uint64_t)M, cols, (uint64_t)ldc, 32)) return -1;
       return launch_gemm_tc_ts<BN, STAGES, EPI, true>(ma, mw, mc, C, ldc, M, N, K, status, s);
     }
@@ -568,7 +576,7 @@ static int launch_gemm_pair(const CUtensorMap& ma, const void* W, long ldw, void
     if (hb_make_tensor_map_f32_box32(&mc, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc)) return -1;
   } else {
     if (((uintptr_t)C & 15) || (ldc & 7)) HB_FAIL("hb_gemm_tc: the CTA-pair kernel needs a 16-byte aligned C");
-    const uint64_t cols = EPI == EPI_SWIGLU_BF16 ? (uint64_t)N / 2 : (uint64_t)N;
+    const uint64_t cols = EPI_IS_GLU(EPI) ? (uint64_t)N / 2 : (uint64_t)N;
     if (hb_make_tensor_map_bf16(&mc, C, (uint64_t)M, cols, (uint64_t)ldc, 32)) return -1;
   }
   auto kern = gemm_tc_pair_kernel<6, EPI>;
@@ -592,6 +600,7 @@ static int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mw, v
     case EPI_BF16: return launch_gemm_tc<BN, STAGES, EPI_BF16>(ma, mw, C, ldc, M, N, K, status, s);
     case EPI_ADD_F32: return launch_gemm_tc<BN, STAGES, EPI_ADD_F32>(ma, mw, C, ldc, M, N, K, status, s);
     case EPI_SWIGLU_BF16: return launch_gemm_tc<BN, STAGES, EPI_SWIGLU_BF16>(ma, mw, C, ldc, M, N, K, status, s);
+    case EPI_GEGLU_BF16: return launch_gemm_tc<BN, STAGES, EPI_GEGLU_BF16>(ma, mw, C, ldc, M, N, K, status, s);
   }
   HB_FAIL("hb_gemm_tc: unknown epilogue %d", epi);
 }
@@ -605,7 +614,7 @@ HB_EXPORT int hb_gemm_tc(const void* A, long lda, const void* W, long ldw, void*
                          int epi, int tile_n, int* status, cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7)) HB_FAIL("hb_gemm_tc: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
-  if (epi == EPI_SWIGLU_BF16 && (N & 31)) HB_FAIL("hb_gemm_tc: SwiGLU needs N = %d to be a multiple of 32", N);
+  if (EPI_IS_GLU(epi) && (N & 31)) HB_FAIL("hb_gemm_tc: a gated epilogue needs N = %d to be a multiple of 32", N);
   if (!status) HB_FAIL("hb_gemm_tc: no status word");
   if (tile_n == 0) {
     // 128 x 256 tiles feed the tensor cores best (a narrower tile reads more operand bytes per flop: measured
@@ -631,6 +640,7 @@ HB_EXPORT int hb_gemm_tc(const void* A, long lda, const void* W, long ldw, void*
       case EPI_BF16: r = launch_gemm_pair<EPI_BF16>(ma, W, ldw, C, ldc, M, N, K, status, s); break;
       case EPI_ADD_F32: r = launch_gemm_pair<EPI_ADD_F32>(ma, W, ldw, C, ldc, M, N, K, status, s); break;
       case EPI_SWIGLU_BF16: r = launch_gemm_pair<EPI_SWIGLU_BF16>(ma, W, ldw, C, ldc, M, N, K, status, s); break;
+      case EPI_GEGLU_BF16: r = launch_gemm_pair<EPI_GEGLU_BF16>(ma, W, ldw, C, ldc, M, N, K, status, s); break;
       default: HB_FAIL("hb_gemm_tc: unknown epilogue %d", epi);
     }
     if (r) return r;

@@ -63,8 +63,11 @@ HB_EXPORT int hb_latent_prepare(const float* proj, long ld, int cq_off, int c_of
   return 0;
 }
 
-constexpr int HL_TM = 8, HL_THREADS = 128;
+constexpr int HL_TM = 8, HL_THREADS = 128, HL_TN = 32, HL_KZ = HL_THREADS / HL_TN;
 
+// A block owns HL_TM rows, one head and HL_TN output columns; its threads are HL_TN columns x HL_KZ interleaved slices of
+// k, summed in a fixed order (slice 0 .. HL_KZ - 1) through shared memory: few rows still fill the machine, and a
+// thread's loads of the weight are independent of one another.
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* __restrict__ a, long lda, long a_head,
                                                                   const TW* __restrict__ wt, TO* __restrict__ out, long ldo,
@@ -74,11 +77,13 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
                                                                   const float2* __restrict__ table,
                                                                   const int* __restrict__ row_req,
                                                                   const int* __restrict__ q_len, int row_limit) {
-  extern __shared__ float hl_a[];      // [HL_TM][K + tail]
+  extern __shared__ float hl_a[];      // [HL_TM][K + tail], then [HL_KZ][HL_TM][HL_TN] partial sums
   hb_pdl_launch();
   hb_pdl_wait();
-  const int h = blockIdx.y, t0 = blockIdx.z * HL_TM, n = blockIdx.x * HL_THREADS + threadIdx.x;
+  const int h = blockIdx.y, t0 = blockIdx.z * HL_TM, nl = threadIdx.x % HL_TN, kz = threadIdx.x / HL_TN;
+  const int n = blockIdx.x * HL_TN + nl;
   const int KT_ = K + tail, rows = min(HL_TM, T - t0);
+  float* red = hl_a + HL_TM * KT_;
   // rows of requests that bring row_limit rows or more belong to another path: a block all of whose rows do is idle
   unsigned skip = 0;
   if (q_len)
@@ -89,25 +94,32 @@ __global__ void __launch_bounds__(HL_THREADS) heads_linear_kernel(const float* _
     hl_a[r * KT_ + k] = a[(size_t)(t0 + r) * lda + (size_t)h * a_head + k];
   }
   __syncthreads();
-  if (n < N) {
-    float acc[HL_TM];
+  float acc[HL_TM];
 #pragma unroll
-    for (int r = 0; r < HL_TM; r++) acc[r] = 0.f;
+  for (int r = 0; r < HL_TM; r++) acc[r] = 0.f;
+  if (n < N) {
     const TW* w = wt + (size_t)h * K * N + n;
-    for (int k = 0; k < K; k++) {
+#pragma unroll 4
+    for (int k = kz; k < K; k += HL_KZ) {
       const float wv = hb_to_float(w[(size_t)k * N]);
 #pragma unroll
       for (int r = 0; r < HL_TM; r++) acc[r] = fmaf(hl_a[r * KT_ + k], wv, acc[r]);
     }
+  }
 #pragma unroll
-    for (int r = 0; r < HL_TM; r++) {
-      if (r >= rows) break;
+  for (int r = 0; r < HL_TM; r++) red[(kz * HL_TM + r) * HL_TN + nl] = acc[r];
+  __syncthreads();
+  if (n < N) {
+    // thread (nl, kz) finishes rows kz, kz + HL_KZ, ...
+    for (int r = kz; r < rows; r += HL_KZ) {
       if (skip >> r & 1) continue;
-      float o = acc[r];
+      float o = 0.f;
+#pragma unroll
+      for (int z = 0; z < HL_KZ; z++) o += red[(z * HL_TM + r) * HL_TN + nl];
       if (gate) o *= 1.f / (1.f + expf(-gate[(size_t)(t0 + r) * ld_gate + gate_off + (size_t)h * N + n]));
       out[(size_t)(t0 + r) * ldo + (size_t)h * o_head + n] = hb_from_float<TO>(o);
     }
-  } else if (n < N + tail) {
+  } else if (n < N + tail && kz == 0) {
     const int j = n - N, half = rot >> 1;
     for (int r = 0; r < rows; r++) {
       if (skip >> r & 1) continue;
@@ -132,10 +144,10 @@ HB_EXPORT int hb_heads_linear(const float* a, long lda, long a_head, const void*
                               cudaStream_t s) {
   if (T <= 0 || H <= 0) return 0;
   if (tail && (!pos || !table || rot > tail || (rot & 1))) HB_FAIL("hb_heads_linear: a rotated tail needs positions and a table");
-  const size_t smem = (size_t)HL_TM * (K + tail) * sizeof(float);
+  const size_t smem = ((size_t)HL_TM * (K + tail) + (size_t)HL_KZ * HL_TM * HL_TN) * sizeof(float);
   if (smem > 96 * 1024) HB_FAIL("hb_heads_linear: K = %d is too wide", K);
   if ((T + HL_TM - 1) / HL_TM > 65535 || H > 65535) HB_FAIL("hb_heads_linear: the grid is too large");
-  dim3 grid((N + tail + HL_THREADS - 1) / HL_THREADS, H, (T + HL_TM - 1) / HL_TM);
+  dim3 grid((N + tail + HL_TN - 1) / HL_TN, H, (T + HL_TM - 1) / HL_TM);
 #define HL_LAUNCH(TW, TO)                                                                                       \
   do {                                                                                                          \
     auto kern = heads_linear_kernel<TW, TO>;                                                                    \

@@ -43,7 +43,7 @@ _fns = {}
 _LAUNCHES = {"hb_rows_scaled_qkv_rope": 1, "hb_rows_scaled_swiglu": 1, "hb_rows_norm_qkv_rope": 1, "hb_rows_add": 1, "hb_rows_norm_swiglu": 1, "hb_gemm_tc_rope_kv": 1, "hb_gemm_stream_finish": 1, "hb_add_rmsnorm_slices": 1, "hb_rope_kv_slices": 1, "hb_gemm_tc": 1, "hb_gemm_stream": 1, "hb_attn_decode": 1, "hb_flash_prefill": 1, "hb_flash_prefill_tc": 1}
 _status = None
 
-EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16, EPI_SLICES = 0, 1, 2, 3, 4
+EPI_F32, EPI_BF16, EPI_ADD_F32, EPI_SWIGLU_BF16, EPI_SLICES, EPI_GEGLU_BF16 = 0, 1, 2, 3, 4, 5
 
 
 class KernelTimeout(RuntimeError):
@@ -277,8 +277,13 @@ def linear_swiglu(a, w, act_out, group) -> bool:
 
 
 def linear_gated(a, w, act_out, group, act) -> bool:
-    """The gate/up product with the activation in its epilogue: "silu" only so far."""
-    return act == "silu" and linear_swiglu(a, w, act_out, group)
+    """The gate/up product with the activation ("silu" or "gelu_tanh") in its epilogue (csrc/gemm_tc.cu, gemm_stream.cu)."""
+    if act == "silu":
+        return linear_swiglu(a, w, act_out, group)
+    if act != "gelu_tanh" or group != 16 or act_out.dtype != torch.bfloat16 or not _tc_ok(a, w.t) or w.shape[0] % 32:
+        return False
+    _gemm(a, w.t, act_out, EPI_GEGLU_BF16)
+    return True
 
 
 # ------------------------------------------------------------------------------------------

@@ -559,6 +559,14 @@ def linear(a: torch.Tensor, w: Weight, out: torch.Tensor, accumulate: bool = Fal
     return gemm_plain(a, w.t, out, accumulate)
 
 
+def linear_into_stream(a: torch.Tensor, w: Weight, x: torch.Tensor) -> torch.Tensor:
+    """x += a @ w.T into the float32 residual stream: for a few bfloat16 rows one kernel that owns whole-K stripes of the
+    output (nothing left to add across blocks), else the product `linear` chooses."""
+    if a.is_cuda and a.dtype == torch.bfloat16 and linear_add_rows(a, w, x):
+        return x
+    return linear(a, w, x, accumulate=True)
+
+
 def linear_scaled_add(a: torch.Tensor, w: Weight, x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """x[m, n] += scale[n] * (a @ w.T)[m, n]: an output projection times the layer's scale vector, added into the float32
     residual stream. One kernel with the plain product; the tensor-core product leaves its float32 result to a small

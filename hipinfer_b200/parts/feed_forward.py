@@ -103,7 +103,7 @@ class GatedFF(Part):
             ops.linear(xn, self.wgu, gu)
             ops.gated_act(gu, act, self.group, self.act)
         planes.record(batch, "activation", act)
-        ops.linear(act, self.wdown, x, accumulate=True)
+        ops.linear_into_stream(act, self.wdown, x)
         return None
 
 

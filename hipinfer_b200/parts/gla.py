@@ -78,7 +78,7 @@ class GatedLinearAttentionMixer(Mixer):
         ops.gla(proj, (0, HD, 2 * HD, 2 * HD + HE), z, self.a_bias, self.norm_w, state["S"], batch, y, self.heads, self.dim,
                 self.vdim, self.tau, self.eps)
         planes.record(batch, "attention", y)
-        ops.linear(y, self.wo, x, accumulate=True)
+        ops.linear_into_stream(y, self.wo, x)
         return None
 
 

@@ -121,7 +121,7 @@ class LatentAttentionMixer(Mixer):
             planes.record(batch, "q", qb)
             if len(many) == batch.n_requests:
                 planes.record(batch, "attention", att)
-                ops.linear(att, self.wo, x, accumulate=True)
+                ops.linear_into_stream(att, self.wo, x)
                 return None
         limit = ops.MASKED_FLASH_MIN_ROWS if many else 0
         qa = torch.empty(T, H * (R + Dr), dtype=self.ctx.dtype, device=dev)        # per head [Wuk^T q_plain | rotated part]
@@ -134,7 +134,7 @@ class LatentAttentionMixer(Mixer):
         if not many:
             planes.record(batch, "q", qa)
         planes.record(batch, "attention", att)
-        ops.linear(att, self.wo, x, accumulate=True)
+        ops.linear_into_stream(att, self.wo, x)
         return None
 
 

@@ -140,7 +140,7 @@ class MaskedAttentionMixer(Mixer):
                              gate_per_head=self.gate == "head")
         planes.record(batch, "q", q)
         planes.record(batch, "attention", att)
-        ops.linear(att, self.wo, x, accumulate=True)
+        ops.linear_into_stream(att, self.wo, x)
         return None
 
 
