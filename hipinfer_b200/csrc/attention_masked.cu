@@ -275,7 +275,7 @@ HB_EXPORT int hb_attn_masked(const void* q, int q_dt, long ldq, const void* kc, 
 #define MA_LAUNCH(TQ, TC, TO)                                                                                      \
   do {                                                                                                             \
     auto kern = attn_masked_rows_kernel<TQ, TC, TO>;                                                               \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
     hb_launch(kern, grid, dim3(MA_THREADS), smem, s, A);                                                           \
   } while (0)
   if (q_dt == HB_F32 && c_dt == HB_F32 && o_dt == HB_F32) MA_LAUNCH(float, float, float);

@@ -309,11 +309,11 @@ HB_EXPORT int hb_attn_masked_flash(const void* q, long ldq, const void* kc, long
     const size_t smem = (size_t)2 * FM_KEYS * ((16 * DK + 8) + (8 * EN + 8)) * sizeof(__nv_bfloat16);                   \
     if (o_dt == HB_BF16) {                                                                                              \
       auto kern = attn_masked_flash_kernel<DK, EN, __nv_bfloat16>;                                                      \
-      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+      if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
       hb_launch(kern, grid, dim3(FM_THREADS), smem, s, A);                                                              \
     } else {                                                                                                            \
       auto kern = attn_masked_flash_kernel<DK, EN, float>;                                                              \
-      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+      if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
       hb_launch(kern, grid, dim3(FM_THREADS), smem, s, A);                                                              \
     }                                                                                                                   \
   }

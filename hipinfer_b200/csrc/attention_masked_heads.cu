@@ -401,11 +401,11 @@ HB_EXPORT int hb_attn_masked_heads(const void* q, long ldq, const void* kc, long
   if (enw == ENW) {                                                                                                 \
     if (o_dt == HB_BF16) {                                                                                          \
       auto kern = attn_masked_heads_kernel<ENW, __nv_bfloat16>;                                                     \
-      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+      if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
       hb_launch(kern, grid, dim3(HS_THREADS), smem, s, A);                                                          \
     } else {                                                                                                        \
       auto kern = attn_masked_heads_kernel<ENW, float>;                                                             \
-      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+      if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
       hb_launch(kern, grid, dim3(HS_THREADS), smem, s, A);                                                          \
     }                                                                                                               \
   }

@@ -218,11 +218,11 @@ HB_EXPORT int hb_gla(const float* proj, long ld, int q_off, int k_off, int v_off
   HB_DISPATCH_2(w_dt, o_dt, "hb_gla", do {                                                                           \
     if (fast) {                                                                                                      \
       auto kern = gla_kernel<DPT, true, TA, TB>;                                                                     \
-      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+      if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
       hb_launch(kern, grid, dim3(threads), smem, s, A);                                                              \
     } else {                                                                                                         \
       auto kern = gla_kernel<DPT, false, TA, TB>;                                                                    \
-      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+      if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
       hb_launch(kern, grid, dim3(threads), smem, s, A);                                                              \
     }                                                                                                                \
   } while (0))

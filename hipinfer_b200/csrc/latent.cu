@@ -151,7 +151,7 @@ HB_EXPORT int hb_heads_linear(const float* a, long lda, long a_head, const void*
 #define HL_LAUNCH(TW, TO)                                                                                       \
   do {                                                                                                          \
     auto kern = heads_linear_kernel<TW, TO>;                                                                    \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+    if (smem + 4096 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
     hb_launch(kern, grid, dim3(HL_THREADS), smem, s, a, lda, a_head, (const TW*)wt, (TO*)out, ldo, o_head, T, K, N, gate,  \
               ld_gate, gate_off, tail, rot, pos, (const float2*)table, row_req, q_len, row_limit);              \
   } while (0)

@@ -1,6 +1,8 @@
 """The Vegodra design through the engine: the step function, the cache and state manager, trace replay, the scheduler
 and the Python entry point, in 32-bit and in bfloat16, against the plain implementation of tests/plain_vegodra.py, on
 four small configurations of the tests' own (tests/vegodra_models.py)."""
+import math
+
 import pytest
 import torch
 
@@ -225,4 +227,67 @@ def test_pages_behind_every_reader_s_chunk_are_given_back(tmp_path):
     runner = ModelRunner.from_folder(folder, dtype="float32", page_size=16, num_pages=8, max_num_seqs=1)     # 128 tokens of pages
     got = tiny.run_plan(tiny.RunnerStepper(runner), {"x": toks}, [[("x", 50)], [("x", 30)]] + [[("x", 1)]] * 40 + [[("x", 60)]] * 3)
     _close(got["x"], ref, "float32", "300 tokens through 128 tokens of pages")
+    assert not runner.live_requests()
+
+
+def _random_config(seed):
+    """A configuration drawn from sizes that resemble real layers in the small: every kind of layer at least once, in a
+    random order, a reader where an attention layer precedes it."""
+    import random
+
+    rng = random.Random(seed)
+    pick = rng.choice
+    width = pick([64, 96, 128, 160, 192, 256])
+    layers, owners = [], []
+    kinds = ["latent", "attn", "gla"] + [pick(["latent", "attn", "gla", "reader"]) for _ in range(rng.randint(1, 4))]
+    rng.shuffle(kinds)
+    attn_shape = None
+    for kind in kinds:
+        ff = pick([None, 64, 96, 256, 320])
+        if kind == "reader" and not owners:
+            kind = "attn"
+        if kind == "latent":
+            rot_dim = pick([8, 16, 32, 64])
+            layers.append(tm.latent(pick([1, 2, 3, 4, 6, 8]), pick([16, 32, 48, 64, 96, 128]), rot_dim, pick([16, 32, 48, 64, 96, 128]),
+                                    pick([24, 48, 80, 128]), pick([32, 64, 96, 128, 192, 256]), ff=ff, dims=pick([rot_dim, rot_dim // 2]),
+                                    base=pick([100.0, 10000.0, 500000.0])))
+        elif kind == "gla":
+            layers.append(tm.gla(pick([1, 2, 4]), pick([16, 32, 48, 64, 128]), pick([16, 32, 64, 128]), pick([1.0, 4.0, 16.0]), ff=ff,
+                                 rank=pick([4, 16, 24])))
+        elif kind == "attn":
+            kv = pick([1, 2, 4])
+            dim = pick([16, 32, 64, 128])
+            attn_shape = dict(heads=kv * pick([1, 2, 3, 4]), kv_heads=kv, dim=dim, vdim=pick([16, 32, 64, 128]), dims=pick([dim, dim // 2, dim // 4]),
+                              base=pick([10000.0, 1000000.0]), scale=pick([0.125, 0.3, 1.0 / math.sqrt(dim)]))
+            owners.append((len(layers), attn_shape))
+            layers.append(tm.attn(chunk=pick([None, 16, 33, 64, 96, 128]), ff=ff, **attn_shape))
+        else:
+            src, shape = pick(owners)
+            layers.append(tm.attn(chunk=pick([None, 16, 33, 64, 96, 128]), kv_from=src, ff=ff, **shape))
+    return tm.model(pick([64, 97, 300, 576]), width, layers, eps=pick([1e-5, 1e-6]), max_positions=512)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", list(range(24)))
+def test_random_configurations(seed, dtype, tmp_path):
+    """Two dozen configurations drawn at random (sizes on either side of every kernel's size steps): whole prompts, the last
+    tokens one by one, portions, and a mixed batch, against the plain model."""
+    import math as _math  # noqa: F401
+    from hipinfer_b200.engine.runner import ModelRunner
+
+    cfg = _random_config(seed)
+    folder, cfg, w = tm.make_folder(tmp_path / "m", cfg, seed=seed, dtype=torch.float32 if dtype == "float32" else torch.bfloat16)
+    reqs = {"a": tiny.random_tokens(170, cfg["vocab"], 1), "b": tiny.random_tokens(41, cfg["vocab"], 2), "c": tiny.random_tokens(1, cfg["vocab"], 3)}
+    model = plain.PlainVegodra(cfg, w)
+    ref = {}
+    for rid, toks in reqs.items():
+        model.reset()
+        ref[rid] = model.forward(toks)
+    runner = ModelRunner.from_folder(folder, dtype=dtype, page_size=16, num_pages=30, max_num_seqs=3)
+    st = tiny.RunnerStepper(runner)
+    for plan in (tiny.plan_whole(reqs), tiny.plan_tail_decode(reqs, 24), tiny.plan_portions(reqs, (17, 2, 40, 1, 33)),
+                 tiny.plan_mixed(reqs, seed, max_live=3)):
+        got = tiny.run_plan(st, reqs, plan)
+        for rid in reqs:
+            _close(got[rid], ref[rid], dtype, f"random configuration {seed} {rid}")
     assert not runner.live_requests()

@@ -376,3 +376,28 @@ def test_masked_attention_portions_on_tensor_cores(case):
                              None if gate is None else gate[t, 8:].double(), gate_kind == "head")
         close(out[t], want, dtype, f"row {t} (request {r}, position {p})")
         close(rows_only[t], want, dtype, f"row kernel, row {t}")
+
+
+@pytest.mark.parametrize("H,D,E", [(6, 160, 128), (32, 288, 256), (3, 48, 32), (16, 80, 64), (1, 32, 16), (40, 96, 64)])
+def test_single_rows_whose_values_are_a_prefix_of_the_key_rows(H, D, E):
+    """Latent attention's pass over the cache: one kv head, keys D wide, values their first E columns (one plane), 32-bit
+    result; rows at the first positions, at tile and split borders and far in; sizes on both sides of the kernels'
+    shared-memory steps and head tiles."""
+    from hipinfer_b200.kernels import ops
+
+    dtype, ps, scale = torch.bfloat16, 16, 1.3 / math.sqrt(D)
+    lens = [530, 70]
+    keys = [rnd(n, 1, D, seed=10 + r) for r, n in enumerate(lens)]
+    kc, _, bt = _paged(keys, [k[..., :E] for k in keys], ps, dtype, seed=3, alias=True)
+    rows = [(0, p) for p in (0, 1, 63, 64, 255, 256, 257, 511, 512, 529)] + [(1, p) for p in (0, 15, 16, 69)]
+    T = len(rows)
+    q = rnd(T, H * D, seed=5)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    batch = SimpleNamespace(block_tables=[bt], row_request=i32([r for r, _ in rows]), positions=i32([p for _, p in rows]), max_pos=max(lens) - 1)
+    for plain_kernel in (False, True):
+        out = torch.empty(T, H * E, dtype=torch.float32, device=DEV)
+        ops.attention_masked(q.to(dtype).to(DEV), kc, kc, batch, 0, out, H, 1, D, E, ps, scale, "causal", force_plain=plain_kernel)
+        for t, (r, p) in enumerate(rows):
+            kk = keys[r].to(dtype).double()
+            want = _attend_plain(q[t].to(dtype).double().view(H, D), kk, kk[..., :E], p, H, 1, scale, "causal", 0, 0, 0, None, None, False)
+            close(out[t], want, dtype, f"row {t} (request {r}, position {p}, plain kernel {plain_kernel})")
