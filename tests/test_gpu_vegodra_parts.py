@@ -134,7 +134,7 @@ def _attend_plain(q, k, v, p, H, G, scale, mask, window, keep, chunk, sink, gate
 
 
 CASES = [  # H, G, D, E, mask, window, keep, chunk, sink, gate, lengths
-    (6, 2, 64, 64, "chunk", 0, 0, 96, True, "head", [400, 97]),
+    (8, 2, 64, 64, "chunk", 0, 0, 80, True, "head", [400, 97]),
     (4, 4, 8, 8, "chunk", 0, 0, 1, True, "head", [40, 3]),
     (3, 1, 10, 6, "chunk", 0, 0, 5, False, "none", [33]),
     (8, 2, 32, 48, "chunk", 0, 0, 70, True, "element", [700, 150]),
@@ -210,7 +210,7 @@ def test_a_far_key_dominates_and_a_key_outside_the_chunk_does_not_leak(dtype):
 
 # ------------------------------------------------------------------------------------------ latent attention
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Rq,R,Dr,rot", [(80, 128, 32, 32), (14, 20, 6, 4), (300, 520, 64, 64)])
+@pytest.mark.parametrize("Rq,R,Dr,rot", [(72, 136, 32, 32), (14, 20, 6, 4), (300, 520, 64, 64)])
 def test_latents_into_the_cache(dtype, Rq, R, Dr, rot):
     from hipinfer_b200.kernels import ops
 
@@ -276,7 +276,7 @@ def _gla_plain(proj, z, ab, nw, state, lens, slots, H, D, E, tau, eps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,D,E,tau", [(4, 48, 32, 16.0), (2, 128, 128, 4.0), (3, 10, 6, 1.0), (1, 64, 256, 2.0), (2, 200, 24, 8.0)])
+@pytest.mark.parametrize("H,D,E,tau", [(4, 48, 24, 8.0), (2, 128, 128, 4.0), (3, 10, 6, 1.0), (1, 64, 256, 2.0), (2, 200, 24, 8.0), (2, 64, 64, 16.0)])
 def test_gated_linear_attention(dtype, H, D, E, tau):
     from hipinfer_b200.kernels import ops
 
@@ -335,7 +335,7 @@ def test_a_decay_of_one_keeps_and_a_decay_of_zero_forgets():
             close(out[t], o / o.pow(2).mean().sqrt() * 30.0, torch.float32, f"token {t}, z = {zval}")
 
 
-@pytest.mark.parametrize("case", [(6, 2, 64, 64, "chunk", 0, 0, 96, True, "head"), (8, 2, 128, 128, "chunk", 0, 0, 200, True, "element"),
+@pytest.mark.parametrize("case", [(12, 4, 64, 64, "chunk", 0, 0, 112, True, "head"), (8, 2, 128, 128, "chunk", 0, 0, 200, True, "element"),
                                   (4, 4, 64, 48, "causal", 0, 0, 0, False, "element"), (4, 1, 32, 32, "window", 70, 5, 0, True, "head"),
                                   (2, 2, 48, 32, "chunk", 0, 0, 64, False, "none")],
                          ids=lambda c: f"{c[4]}{c[7] or c[5] or ''}-h{c[0]}g{c[1]}-d{c[2]}e{c[3]}")
@@ -378,7 +378,7 @@ def test_masked_attention_portions_on_tensor_cores(case):
         close(rows_only[t], want, dtype, f"row kernel, row {t}")
 
 
-@pytest.mark.parametrize("H,D,E", [(6, 160, 128), (32, 288, 256), (3, 48, 32), (16, 80, 64), (1, 32, 16), (40, 96, 64)])
+@pytest.mark.parametrize("H,D,E", [(5, 160, 64), (32, 288, 256), (3, 48, 32), (16, 80, 64), (1, 32, 16), (40, 96, 64), (9, 176, 128)])
 def test_single_rows_whose_values_are_a_prefix_of_the_key_rows(H, D, E):
     """Latent attention's pass over the cache: one kv head, keys D wide, values their first E columns (one plane), 32-bit
     result; rows at the first positions, at tile and split borders and far in; sizes on both sides of the kernels'
