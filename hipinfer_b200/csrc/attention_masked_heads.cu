@@ -8,9 +8,9 @@
 // beside the traffic), keeps the online softmax of its rows in registers, and accumulates its slice of O. Queries lie
 // in shared memory (any D that is a multiple of 16), key and value tiles of 64 ABSOLUTE positions come by cp.async,
 // double-buffered; the values may be the first E columns of the key rows (a latent that serves as both), in which case
-// no value tile is loaded. A row's visible tiles are split HS_SPLIT_TILES a CTA (a matter of its position alone); the
-// CTA that arrives last at (row, kv head, head tile) joins the partial results in the splits' order, adds the sink,
-// applies the gate and writes.
+// no value tile is loaded. A row's visible tiles are split HS_SPLIT_TILES a CTA (a matter of its position alone). A
+// row that one CTA walks is finished by it (sink, gate, one rounding); the partial results of a row that several walk
+// are joined, in the splits' order, by a second kernel over the whole machine.
 #include "common.cuh"
 
 #define HK 64
@@ -60,7 +60,6 @@ __device__ __forceinline__ int hs_tile_at(int i, int lo, int keep) {
 template <int ENW, typename TO>
 __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs A) {
   extern __shared__ __align__(16) uint8_t hs_smem[];
-  __shared__ int last_flag;
   hb_pdl_launch();
   hb_pdl_wait();
   const int g = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, quad = lane >> 2, qi = lane & 3;
@@ -236,24 +235,10 @@ __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs
     stage[ra * RS + E] = m_a; stage[ra * RS + E + 1] = l_a;
     stage[rb * RS + E] = m_b; stage[rb * RS + E + 1] = l_b;
   }
+  if (n_splits_row > 1) return;            // the merge kernel joins the splits of such a row
   const float* all = stage;
-  int n_parts = 1;
-  if (n_splits_row > 1) {
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const int n = atomicAdd(A.arrived + slot, 1);
-      last_flag = n == n_splits_row - 1;
-      if (last_flag) A.arrived[slot] = 0;
-    }
-    __syncthreads();
-    if (!last_flag) return;
-    __threadfence();
-    all = A.part + slot * A.splits * (size_t)MR * RS;
-    n_parts = n_splits_row;
-  } else {
-    __syncthreads();
-  }
+  const int n_parts = 1;
+  __syncthreads();
   const size_t pstride = (size_t)MR * RS;
   // every head's factor for each split (exp of the split's maximum against the row's, over the weight sum with the sink,
   // times the head's gate) first, into shared memory behind the staged sums; then every (head, 4 columns) is one
@@ -323,6 +308,60 @@ __global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_kernel(HeadsArgs
       ((TO*)A.out)[(size_t)t * A.ldo + head * E + e] = hb_from_float<TO>(a);
     }
   }
+}
+
+// Joins the key splits of rows that were walked by several CTAs: one thread a (head, 4 value columns). It finds the row's
+// maximum and weight sum over the splits (a few cached loads), adds the sink, and sums the splits' columns times
+// exp2(split maximum - row maximum) in the splits' order, all loads independent of one another; gate and one rounding
+// on the way out. The whole machine takes part: the partial sums of a latent layer's row are as large as a third of
+// the keys it read, too much for one CTA to pull through its own loads.
+template <typename TO>
+__global__ void __launch_bounds__(HS_THREADS) attn_masked_heads_merge_kernel(HeadsArgs A) {
+  hb_pdl_launch();
+  hb_pdl_wait();
+  const int t = blockIdx.z, ZT = gridDim.y / A.G, g = blockIdx.y / ZT, z = blockIdx.y % ZT;
+  if (A.q_len && A.q_len[A.row_req[t]] >= A.row_limit) return;
+  const int E = A.E, MR = 16 * A.MT, HG = A.H / A.G, RS = E + 4, C4 = E / 4;
+  const int h0 = z * MR, nh = min(MR, HG - h0);
+  const int p = A.pos[t];
+  int lo = 0, keep = 0;
+  if (A.mask == 1 && A.window > 0) { lo = max(0, p - A.window + 1); keep = min(A.keep_first, p + 1); }
+  else if (A.mask == 2 && A.chunk > 0) lo = (p / A.chunk) * A.chunk;
+  const int n_parts = (hs_tile_count(p, lo, keep) + HS_SPLIT_TILES - 1) / HS_SPLIT_TILES;
+  if (n_parts <= 1) return;                                   // finished by the CTA that walked it
+  const int i = blockIdx.x * HS_THREADS + threadIdx.x;
+  if (i >= nh * C4) return;
+  const int r = i / C4, e = (i - r * C4) * 4;
+  const size_t slot = ((size_t)t * A.G + g) * ZT + z, pstride = (size_t)MR * RS;
+  const float* all = A.part + slot * A.splits * pstride + (size_t)r * RS;
+  const size_t head = (size_t)g * HG + h0 + r;
+  float m = -INFINITY;
+  for (int sp = 0; sp < n_parts; sp++) m = fmaxf(m, all[sp * pstride + E]);
+  float l = 0.f;
+  for (int sp = 0; sp < n_parts; sp++) l = fmaf(all[sp * pstride + E + 1], exp2f(all[sp * pstride + E] - m), l);
+  float f = 1.f;
+  if (A.sink) {
+    const float sk = A.sink[head] * 1.4426950408889634f, m2 = fmaxf(m, sk);     // the maxima are in units of log 2
+    f = exp2f(m - m2);
+    l = fmaf(l, f, exp2f(sk - m2));
+  }
+  f = l > 0.f ? f / l : 0.f;
+  if (A.gate_mode == 2) f *= 1.f / (1.f + expf(-A.gate[(size_t)t * A.ld_gate + A.gate_off + head]));
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+  for (int sp = 0; sp < n_parts; sp++) {
+    const float4 v = *(const float4*)(all + sp * pstride + e);
+    const float w = exp2f(all[sp * pstride + E] - m);
+    a.x = fmaf(v.x, w, a.x); a.y = fmaf(v.y, w, a.y); a.z = fmaf(v.z, w, a.z); a.w = fmaf(v.w, w, a.w);
+  }
+  a.x *= f; a.y *= f; a.z *= f; a.w *= f;
+  if (A.gate_mode == 1) {
+    const float* gp = A.gate + (size_t)t * A.ld_gate + A.gate_off + head * E + e;
+    a.x *= 1.f / (1.f + expf(-gp[0])); a.y *= 1.f / (1.f + expf(-gp[1]));
+    a.z *= 1.f / (1.f + expf(-gp[2])); a.w *= 1.f / (1.f + expf(-gp[3]));
+  }
+  TO* op = (TO*)A.out + (size_t)t * A.ldo + head * E + e;
+  op[0] = hb_from_float<TO>(a.x); op[1] = hb_from_float<TO>(a.y); op[2] = hb_from_float<TO>(a.z); op[3] = hb_from_float<TO>(a.w);
 }
 
 static int hs_mt(int HG) { return HG > 16 ? 2 : 1; }
@@ -412,5 +451,11 @@ HB_EXPORT int hb_attn_masked_heads(const void* q, long ldq, const void* kc, long
   HS_LAUNCH(2) HS_LAUNCH(4) HS_LAUNCH(8) HS_LAUNCH(16) HS_LAUNCH(32)
 #undef HS_LAUNCH
   HB_CHECK_LAUNCH("hb_attn_masked_heads");
+  if (A.splits > 1) {
+    dim3 mgrid((16 * A.MT * (E / 4) + HS_THREADS - 1) / HS_THREADS, G * ZT, T);
+    if (o_dt == HB_BF16) hb_launch(attn_masked_heads_merge_kernel<__nv_bfloat16>, mgrid, dim3(HS_THREADS), 0, s, A);
+    else hb_launch(attn_masked_heads_merge_kernel<float>, mgrid, dim3(HS_THREADS), 0, s, A);
+    HB_CHECK_LAUNCH("hb_attn_masked_heads (merge)");
+  }
   return 0;
 }

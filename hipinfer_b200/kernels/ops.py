@@ -567,6 +567,16 @@ def linear_into_stream(a: torch.Tensor, w: Weight, x: torch.Tensor) -> torch.Ten
     return linear(a, w, x, accumulate=True)
 
 
+def linear_rows32(a: torch.Tensor, w: Weight, out: torch.Tensor) -> torch.Tensor:
+    """out = a @ w.T as 32-bit rows for a 32-bit consumer. For a few bfloat16 rows the whole-K rows kernel adds into the
+    zeroed rows (one kernel behind a memset instead of a split-K product and the reduction of its slices); else `linear`."""
+    if a.is_cuda and a.dtype == torch.bfloat16 and out.dtype == torch.float32 and out.is_contiguous() and a.shape[0] <= 8:
+        out.zero_()
+        if linear_add_rows(a, w, out):
+            return out
+    return linear(a, w, out)
+
+
 def linear_scaled_add(a: torch.Tensor, w: Weight, x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """x[m, n] += scale[n] * (a @ w.T)[m, n]: an output projection times the layer's scale vector, added into the float32
     residual stream. One kernel with the plain product; the tensor-core product leaves its float32 result to a small

@@ -71,7 +71,7 @@ class GatedLinearAttentionMixer(Mixer):
     def forward(self, xn, x, batch, cache, state):
         T, HD, HE = xn.shape[0], self.heads * self.dim, self.heads * self.vdim
         proj = torch.empty(T, 2 * HD + 2 * HE + self.rank, dtype=torch.float32, device=xn.device)
-        ops.linear(xn, self.w_in, proj)
+        ops.linear_rows32(xn, self.w_in, proj)
         z = torch.empty(T, HD, dtype=torch.float32, device=xn.device)
         ops.linear(proj[:, 2 * HD + 2 * HE:], self.w_a2, z)      # the rank is small: 32-bit rows, the plain product
         y = torch.empty(T, HE, dtype=self.ctx.dtype, device=xn.device)

@@ -94,14 +94,14 @@ class LatentAttentionMixer(Mixer):
         T, H, dev = xn.shape[0], self.heads, xn.device
         Rq, R, Dr, D, E = self.q_rank, self.kv_rank, self.rot_dim, self.dim, self.vdim
         proj = torch.empty(T, Rq + R + Dr + H * E, dtype=torch.float32, device=dev)
-        ops.linear(xn, self.w_in, proj)
+        ops.linear_rows32(xn, self.w_in, proj)
         ckr = cache.planes["ckr"]
         cq = torch.empty(T, Rq, dtype=self.ctx.dtype, device=dev)
         ops.latent_prepare(proj, (0, Rq, Rq + R), self.wq_norm, self.wc_norm, batch.positions,
                            batch.slot_maps[cache.group] if cache.write else None, self.table, self.rot_dims, self.eps, cq, ckr,
                            Rq, R, Dr, self.ctx.page_size)
         q = torch.empty(T, H * (D + Dr), dtype=torch.float32, device=dev)
-        ops.linear(cq, self.w_uq, q)
+        ops.linear_rows32(cq, self.w_uq, q)
         att = torch.empty(T, H * E, dtype=self.ctx.dtype, device=dev)
         # requests that bring many rows: keys and values of their whole context from one product, tensor-core attention
         many = [r for r in range(batch.n_requests) if batch.h_q_len[r] >= ops.MASKED_FLASH_MIN_ROWS] \

@@ -126,7 +126,7 @@ class MaskedAttentionMixer(Mixer):
     def forward(self, xn, x, batch, cache, state):
         T = xn.shape[0]
         proj = torch.empty(T, self.n_q + self.n_kv + self.n_gate, dtype=torch.float32, device=xn.device)
-        ops.linear(xn, self.w_in, proj)
+        ops.linear_rows32(xn, self.w_in, proj)
         q = torch.empty(T, self.n_q, dtype=self.ctx.dtype, device=xn.device)
         write = cache.write and not self.reads_cache
         ops.rope_norm_store(proj, (0, self.n_q, self.n_q + self.kv_heads * self.dim), batch.positions,
