@@ -30,7 +30,6 @@ struct HeadsArgs {
   float scale;
   const int* q_len; int row_limit;
   float* part;                          // [T][G][ZT][splits][16 MT][E + 4]
-  int* arrived;                         // [T][G][ZT]
   int splits;
 };
 
@@ -402,17 +401,12 @@ HB_EXPORT long hb_attn_masked_heads_workspace(int T, int H, int G, int E, int ma
   if (splits <= 1) return 0;
   return (long)T * G * ZT * splits * 16 * MT * (E + 4);
 }
-HB_EXPORT int hb_attn_masked_heads_counters(int T, int H, int G) {
-  const int HG = H / G, MT = hs_mt(HG), ZT = (HG + 16 * MT - 1) / (16 * MT);
-  return T * G * ZT;
-}
-
 HB_EXPORT int hb_attn_masked_heads(const void* q, long ldq, const void* kc, long k_page, long k_head, long k_row, const void* vc,
                                    long v_page, long v_head, long v_row, int alias, const int* bt, int bt_stride,
                                    const int* row_req, const int* pos, const float* sink, const float* gate, long ld_gate,
                                    int gate_off, int gate_mode, void* out, int o_dt, long ldo, int T, int H, int G, int D, int E,
                                    int page_size, int mask, int window, int keep_first, int chunk, float scale, const int* q_len,
-                                   int row_limit, float* part, long n_part, int* arrived, int max_pos, cudaStream_t s) {
+                                   int row_limit, float* part, long n_part, int max_pos, cudaStream_t s) {
   if (T <= 0) return 0;
   const int enw = hs_enw(H, G, D, E, alias);
   if (!enw) HB_FAIL("hb_attn_masked_heads: %d heads over %d kv heads with keys of %d and values of %d are not sizes it takes", H, G, D, E);
@@ -425,13 +419,13 @@ HB_EXPORT int hb_attn_masked_heads(const void* q, long ldq, const void* kc, long
   A.bt_stride = bt_stride; A.row_req = row_req; A.pos = pos; A.sink = sink; A.gate = gate; A.ld_gate = ld_gate; A.gate_off = gate_off;
   A.gate_mode = gate ? gate_mode : 0; A.out = out; A.ldo = ldo; A.H = H; A.G = G; A.D = D; A.E = E; A.page_size = page_size;
   A.mask = mask; A.window = window; A.keep_first = keep_first; A.chunk = chunk; A.scale = scale; A.q_len = q_len;
-  A.row_limit = row_limit; A.part = part; A.arrived = arrived;
+  A.row_limit = row_limit; A.part = part;
   const int HG = H / G;
   A.MT = hs_mt(HG);
   const int ZT = (HG + 16 * A.MT - 1) / (16 * A.MT);
   A.splits = hs_splits(mask, window, keep_first, chunk, max_pos);
   if (A.splits < 1) A.splits = 1;
-  if (A.splits > 1 && (!part || !arrived || n_part < (long)T * G * ZT * A.splits * 16 * A.MT * (E + 4)))
+  if (A.splits > 1 && (!part || n_part < (long)T * G * ZT * A.splits * 16 * A.MT * (E + 4)))
     HB_FAIL("hb_attn_masked_heads: rows of up to %d key tiles need a workspace", A.splits * HS_SPLIT_TILES);
   if ((long)ZT * A.splits > 65535) HB_FAIL("hb_attn_masked_heads: the grid is too large");
   const size_t smem = hs_smem_bytes(A.MT, D, E, alias);

@@ -51,7 +51,7 @@ _SIGS = {
         "hb_attn_masked_flash_supported": [_i, _i],
         "hb_attn_masked_heads_supported": [_i, _i, _i, _i, _i],
         "hb_attn_masked_heads": [_p, _l, _p, _l, _l, _l, _p, _l, _l, _l, _i, _p, _i, _p, _p, _p, _p, _l, _i, _i, _p, _i, _l, _i, _i,
-                                 _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _l, _p, _i, _p],
+                                 _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _l, _i, _p],
         "hb_attn_masked_flash": [_p, _l, _p, _l, _l, _l, _p, _l, _l, _l, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _p, _l, _i, _i, _p,
                                  _i, _l, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
         "hb_gla": [_p, _l, _i, _i, _i, _i, _p, _l, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _f, _p],
@@ -847,17 +847,15 @@ def attention_masked(q, k_cache, v_cache, batch, group: int, out, n_heads: int, 
         # the heads of a kv head as the rows of warp MMA tiles: a key tile is read once for all of them
         lib.hb_attn_masked_heads_workspace.restype = C.c_long
         lib.hb_attn_masked_heads_workspace.argtypes = [_i] * 9
-        lib.hb_attn_masked_heads_counters.argtypes = [_i] * 3
         n_ws = lib.hb_attn_masked_heads_workspace(T, n_heads, n_kv_heads, vdim, m, int(window), int(keep_first), int(chunk), max_pos)
         ws = torch.empty(n_ws, dtype=torch.float32, device=q.device) if n_ws else None
-        arrived = fast._decode_counters(q.device, lib.hb_attn_masked_heads_counters(T, n_heads, n_kv_heads)) if n_ws else None
         _call("seqmix", "hb_attn_masked_heads", q.data_ptr(), q.stride(0), k_cache.data_ptr(), n_kv_heads * page_size * kw,
               page_size * kw, kw, v_cache.data_ptr(), n_kv_heads * page_size * vw, page_size * vw, vw, 1 if alias else 0,
               bt.data_ptr(), bt.stride(0), batch.row_request.data_ptr(), batch.positions.data_ptr(), _ptr(sink), _ptr(gate),
               gate.stride(0) if gate is not None else 0, int(gate_offset), (2 if gate_per_head else 1) if gate is not None else 0,
               out.data_ptr(), _dt(out), out.stride(0), T, n_heads, n_kv_heads, dim, vdim, page_size, m, int(window),
               int(keep_first), int(chunk), float(scale), batch.req_q_len.data_ptr() if limit else None, limit, _ptr(ws), n_ws,
-              _ptr(arrived), max_pos, _stream())
+              max_pos, _stream())
         return out
     n_ws = lib.hb_attn_masked_workspace(T, n_heads, n_kv_heads, dim, vdim, m, int(window), int(keep_first), int(chunk), max_pos)
     ws = arrived = None
