@@ -272,7 +272,6 @@ def _random_config(seed):
 def test_random_configurations(seed, dtype, tmp_path):
     """Two dozen configurations drawn at random (sizes on either side of every kernel's size steps): whole prompts, the last
     tokens one by one, portions, and a mixed batch, against the plain model."""
-    import math as _math  # noqa: F401
     from hipinfer_b200.engine.runner import ModelRunner
 
     cfg = _random_config(seed)
